@@ -49,14 +49,17 @@ __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log
 
 // ---------------------------------------------------------------- embedding, norms, small element-wise kernels
 
-// x[n] = E[tok[n]] (and a second copy when a looped span re-adds the embedding)
-__global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* tok, int N, int width, float scale) {
+// x[n] = E[tok[n]] * scale (+ P[position of n], a learned position row, not scaled), written to every one of `streams` copies
+// (and a second copy when a looped span re-adds the embedding)
+__global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* tok, int N, int width, float scale, const bf16* pos_table, const int* tpos, int streams) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int n = blockIdx.x;
 	const bf16* e = table + (size_t)tok[n] * width;
+	const bf16* pr = pos_table ? pos_table + (size_t)tpos[n] * width : nullptr;
 	for (int i = threadIdx.x; i < width; i += blockDim.x) {
-		const float v = ldf(e + i) * scale;
-		x[(size_t)n * width + i] = v;
+		float v = ldf(e + i) * scale;
+		if (pr) v += ldf(pr + i);
+		for (int s = 0; s < streams; ++s) x[((size_t)n * streams + s) * width + i] = v;
 		if (x0) x0[(size_t)n * width + i] = v;
 	}
 }
@@ -151,19 +154,20 @@ __global__ void k_seq_cast_cols(AT* out, const float* src, int lds, int col, int
 
 // feed-forward unit on the stacked [gate | up] product.  mode 0: g = min(gate, L), u = clamp(up, -L, L), y = g sigmoid(1.702 g) (u + 1);
 // mode 1: y = silu(gate) up
+// (ld: row stride of gu, 2 * ff when the product holds nothing else)
 template <typename AT>
-__global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limit, int mode) {
+__global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limit, int mode, int ld) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
 	if (i >= (size_t)N * ff) return;
 	const size_t n = i / ff, c = i % ff;
 	if (mode == 1) {
-		const float g = gu[n * 2 * ff + c];
-		out[i] = to_act<AT>(g * sigmoidf_(g) * gu[n * 2 * ff + ff + c]);
+		const float g = gu[n * ld + c];
+		out[i] = to_act<AT>(g * sigmoidf_(g) * gu[n * ld + ff + c]);
 		return;
 	}
-	const float g = fminf(gu[n * 2 * ff + c], limit);
-	const float u = fminf(fmaxf(gu[n * 2 * ff + ff + c], -limit), limit);
+	const float g = fminf(gu[n * ld + c], limit);
+	const float u = fminf(fmaxf(gu[n * ld + ff + c], -limit), limit);
 	out[i] = to_act<AT>(g * sigmoidf_(1.702f * g) * (u + 1.f));
 }
 
@@ -183,6 +187,8 @@ struct ConvArgs {
 	const float* proj;
 	int ldp;
 	const bf16* w;      // [channels][taps]
+	const bf16* bias = nullptr; // [channels] added after the taps, or null
+	int pcol = 0;       // column of channel 0 in the projection (segment columns, weights and state count channels from 0)
 	int taps, channels; // channels = all of q|k|v
 	const float* state; // [slots][taps-1][channels]: the projected values of the taps-1 positions before the step
 	float eps;
@@ -207,9 +213,10 @@ __global__ void k_seq_conv_heads(ConvArgs a, SeqBatch sb) {
 		float y = 0.f;
 		for (int j = 0; j < a.taps; ++j) {
 			const int ago = T1 - j; // tap j multiplies the value `ago` positions back
-			const float v = ago <= back ? a.proj[(size_t)(n - ago) * a.ldp + ch] : st[(size_t)(T1 - (ago - back)) * a.channels + ch];
+			const float v = ago <= back ? a.proj[(size_t)(n - ago) * a.ldp + a.pcol + ch] : st[(size_t)(T1 - (ago - back)) * a.channels + ch];
 			y += ldf(a.w + (size_t)ch * a.taps + j) * v;
 		}
+		if (a.bias) y += ldf(a.bias + ch);
 		if (sg.act) y = y * sigmoidf_(y);
 		d[i] = y;
 		ss += y * y;
@@ -221,7 +228,7 @@ __global__ void k_seq_conv_heads(ConvArgs a, SeqBatch sb) {
 	}
 }
 // after the convolution: the state becomes the last taps-1 projected values of each sequence
-__global__ void k_seq_conv_state(float* state, const float* proj, int ldp, int taps, int channels, SeqBatch sb) {
+__global__ void k_seq_conv_state(float* state, const float* proj, int ldp, int taps, int channels, SeqBatch sb, int pcol) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int b = blockIdx.y, ch = blockIdx.x * blockDim.x + threadIdx.x;
 	if (ch >= channels) return;
@@ -229,7 +236,7 @@ __global__ void k_seq_conv_state(float* state, const float* proj, int ldp, int t
 	float* st = state + (size_t)sb.sslot[b] * T1 * channels;
 	for (int i = 0; i < T1; ++i) { // new[i] = value T1 - i positions before the end; ascending i only reads old[i + cnt] with cnt >= 1
 		const int ago = T1 - i;
-		st[(size_t)i * channels + ch] = ago <= cnt ? proj[(size_t)(start + cnt - ago) * ldp + ch] : st[(size_t)(i + cnt) * channels + ch];
+		st[(size_t)i * channels + ch] = ago <= cnt ? proj[(size_t)(start + cnt - ago) * ldp + pcol + ch] : st[(size_t)(i + cnt) * channels + ch];
 	}
 }
 
@@ -252,6 +259,9 @@ struct AttArgs {
 	int kd, vd;
 	int window;       // <= 0: all earlier positions
 	int keep_first;   // with a window: positions below this stay visible to every later query
+	int chunk = 0;    // > 0: only keys from floor(position / chunk) * chunk on are visible
+	const float* slopes = nullptr; // [heads] or null: score -= slopes[h] * (query position - key position)
+	int add_one = 0;  // 1: a sink of score zero (one added to the denominator); `sink` is then unused
 	float scale;
 	const bf16* sink; // [heads] or null
 	const float* gate;
@@ -273,9 +283,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 	float* lrow = mrow + R;          // [R] running denominator
 	float* frow = lrow + R;          // [R] rescale factor of this chunk
 	__shared__ long rows[ATT_KC];    // cache rows of this chunk's keys
+	__shared__ int dist[ATT_KC];     // distance of each key of the chunk from the query
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = ATT_THREADS / 32;
 	const int slot = sb.tslot[n], pos = sb.tpos[n];
-	const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+	int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+	if (a.chunk > 0) lo = max(lo, pos / a.chunk * a.chunk);
 	// visible keys in order: the kept first positions the window has left behind, [0, kf), then the window [lo, pos]
 	const int kf = min(a.keep_first, lo), total = kf + pos - lo + 1;
 	// this CTA's share of the key chunks (the whole range when nsplit == 1)
@@ -283,8 +295,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 	const int c_begin = (int)blockIdx.z * per * ATT_KC, c_end = min(total - 1, ((int)blockIdx.z + 1) * per * ATT_KC - 1);
 	for (int i = tid; i < R * a.kd; i += ATT_THREADS) qs[i] = a.q[((size_t)n * a.heads + h0) * a.kd + i];
 	if (tid < R) {
-		const bool sk = a.sink && blockIdx.z == 0; // the sink counts once: in the first share
-		mrow[tid] = sk ? ldf(a.sink + h0 + tid) : -INFINITY, lrow[tid] = sk ? 1.f : 0.f;
+		const bool sk = (a.sink || a.add_one) && blockIdx.z == 0; // the sink counts once: in the first share
+		mrow[tid] = sk ? (a.add_one ? 0.f : ldf(a.sink + h0 + tid)) : -INFINITY, lrow[tid] = sk ? 1.f : 0.f;
 	}
 	float acc[ATT_MAXI];
 #pragma unroll
@@ -293,7 +305,10 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 	__syncthreads();
 	for (int c0 = c_begin; c0 <= c_end; c0 += ATT_KC) {
 		const int nk = min(ATT_KC, total - c0);
-		if (tid < ATT_KC) rows[tid] = tid < nk ? cache_row(sb, slot, c0 + tid < kf ? c0 + tid : lo + c0 + tid - kf) : 0;
+		if (tid < ATT_KC) {
+			const int kp = c0 + tid < kf ? c0 + tid : lo + c0 + tid - kf;
+			rows[tid] = tid < nk ? cache_row(sb, slot, kp) : 0, dist[tid] = pos - kp;
+		}
 		__syncthreads();
 		// scores: one warp per key, lanes across the key's channels; the lane's slice of the key is read once for all heads
 		for (int j = warp; j < ATT_KC; j += nwarp) {
@@ -318,14 +333,14 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 						for (int u = 0; u < 4; ++u) dd[u] = warp_sum(dd[u]);
 #pragma unroll
 						for (int u = 0; u < 4; ++u)
-							if (r0 + u < R && lane == u) sc[(r0 + u) * ATT_KC + j] = dd[u] * a.scale;
+							if (r0 + u < R && lane == u) sc[(r0 + u) * ATT_KC + j] = dd[u] * a.scale - (a.slopes ? a.slopes[h0 + r0 + u] * (float)dist[j] : 0.f);
 					}
 				} else {
 					for (int r = 0; r < R; ++r) {
 						float d = 0.f;
 						for (int i = lane; i < a.kd; i += 32) d += qs[r * a.kd + i] * kr[i];
 						d = warp_sum(d);
-						if (lane == 0) sc[r * ATT_KC + j] = d * a.scale;
+						if (lane == 0) sc[r * ATT_KC + j] = d * a.scale - (a.slopes ? a.slopes[h0 + r] * (float)dist[j] : 0.f);
 					}
 				}
 			} else if (lane == 0) {
@@ -483,6 +498,9 @@ struct AttSoftmax {
 	bf16* P;        // same shape
 	int T, C, Cp;
 	int qpos0, k0, window;
+	int chunk = 0;       // > 0: a row sees only positions from floor(position / chunk) * chunk on
+	const float* slopes = nullptr; // already offset to the first head of the launch, or null: score -= slopes[z] * (row position - column position)
+	int add_one = 0;     // 1: one added to the denominator
 	int keep_first, kfb; // columns below kfb are the kept first positions 0 .. kfb-1; column j >= kfb is position k0 + j - kfb
 	float scale;
 	const bf16* sink; // already offset to the first head of the launch, or null
@@ -498,16 +516,19 @@ __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
 	bf16* prow = a.P + ((size_t)z * a.T + t) * a.Cp;
 	const int qpos = a.qpos0 + t;
 	const int hi = min(a.C - 1, qpos - a.k0 + a.kfb); // last visible column
-	const int wlo = a.window > 0 ? qpos - a.window + 1 : 0;
+	int wlo = a.window > 0 ? qpos - a.window + 1 : 0;
+	if (a.chunk > 0) wlo = max(wlo, qpos / a.chunk * a.chunk);
 	const int lo = a.kfb > 0 || a.keep_first > a.k0 ? 0 : max(0, wlo - a.k0); // nothing is visible before this column
 	auto seen = [&](int j) { // column j's position: a kept first token, or inside the window (j <= hi is the causal bound)
 		const int p = j < a.kfb ? j : a.k0 + j - a.kfb;
 		return p >= wlo || p < a.keep_first;
 	};
-	const float sk = a.sink ? ldf(a.sink + z) : -INFINITY;
+	const float sk = a.add_one ? 0.f : a.sink ? ldf(a.sink + z) : -INFINITY;
+	const float slope = a.slopes ? a.slopes[z] : 0.f;
+	auto score = [&](int j) { return srow[j] * a.scale - slope * (float)(qpos - (j < a.kfb ? j : a.k0 + j - a.kfb)); };
 	float mx = sk;
 	for (int j = lo + tid; j <= hi; j += 256)
-		if (seen(j)) mx = fmaxf(mx, srow[j] * a.scale);
+		if (seen(j)) mx = fmaxf(mx, score(j));
 	mx = warp_max(mx);
 	if ((tid & 31) == 0) red[tid >> 5] = mx;
 	__syncthreads();
@@ -519,19 +540,19 @@ __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
 	mx = bc;
 	float sum = 0.f;
 	for (int j = lo + tid; j <= hi; j += 256)
-		if (seen(j)) sum += expf(srow[j] * a.scale - mx);
+		if (seen(j)) sum += expf(score(j) - mx);
 	sum = warp_sum(sum);
 	__syncthreads();
 	if ((tid & 31) == 0) red[tid >> 5] = sum;
 	__syncthreads();
 	if (tid == 0) {
 		for (int w = 1; w < 8; ++w) sum += red[w];
-		if (a.sink) sum += expf(sk - mx);
+		if (a.sink || a.add_one) sum += expf(sk - mx);
 		bc = (a.gate ? sigmoidf_(a.gate[(size_t)t * a.ldg + z]) : 1.f) / sum;
 	}
 	__syncthreads();
 	const float f = bc;
-	for (int j = tid; j < a.Cp; j += 256) prow[j] = __float2bfloat16_rn(j >= lo && j <= hi && seen(j) ? expf(srow[j] * a.scale - mx) * f : 0.f);
+	for (int j = tid; j < a.Cp; j += 256) prow[j] = __float2bfloat16_rn(j >= lo && j <= hi && seen(j) ? expf(score(j) - mx) * f : 0.f);
 }
 
 // ---------------------------------------------------------------- gated delta rule
@@ -912,6 +933,7 @@ struct QkArgs {
 	float* q;           // [N][heads*dim]
 	float* kc;          // cache rows [kv_heads*dim]
 	float* vc;          // cache rows [kv_heads*vdim]
+	int v_norm = 0;     // 1: every value head is divided by its root mean square over vdim (eps inside the root, no weight)
 };
 __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
@@ -958,17 +980,56 @@ __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 		else kd[c] = v;
 	}
 	float* vd = a.vc + row * Vn;
+	if (a.v_norm) { // one warp per value head
+		for (int g = warp; g < a.kv_heads; g += (int)(blockDim.x >> 5)) {
+			const float* src = pr + Q + K + g * a.vdim;
+			float ss = 0.f;
+			for (int i = lane; i < a.vdim; i += 32) ss = fmaf(src[i], src[i], ss);
+			ss = warp_sum(ss);
+			const float rv = 1.f / sqrtf(ss / (float)a.vdim + a.eps);
+			for (int i = lane; i < a.vdim; i += 32) vd[g * a.vdim + i] = src[i] * rv;
+		}
+		return;
+	}
 	for (int i = tid; i < Vn; i += blockDim.x) vd[i] = pr[Q + K + i];
 }
 
 // ---------------------------------------------------------------- routed experts
 // Router: per token the `top` highest-scoring experts (lowest index wins a tie) and a softmax restricted to their scores.  One warp per token.
-__global__ void k_seq_moe_route(const float* logits, int ld, int experts, int top, int N, int* sel, float* wt) {
+// mode 1: scores are a softmax over ALL `experts` router outputs; the choice is made on score + correction (bf16 [experts] or null), the
+// weights are the chosen scores times `scale`, not renormalised.
+__global__ void k_seq_moe_route(const float* logits, int ld, int experts, int top, int N, int* sel, float* wt, int mode, const bf16* correction, float scale) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int n = blockIdx.x * (blockDim.x >> 5) + warp;
 	if (n >= N) return;
 	const float* z = logits + (size_t)n * ld;
+	if (mode == 1) {
+		float mx = -INFINITY;
+		for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
+		mx = warp_max(mx);
+		float den = 0.f;
+		for (int e = lane; e < experts; e += 32) den += expf(z[e] - mx);
+		den = warp_sum(den);
+		for (int k = 0; k < top; ++k) {
+			float bv = -INFINITY, bs = 0.f;
+			int bi = 0x7fffffff;
+			for (int e = lane; e < experts; e += 32) {
+				bool taken = false;
+				for (int j = 0; j < k; ++j) taken |= sel[(size_t)n * top + j] == e;
+				const float sc = expf(z[e] - mx) / den, c = sc + (correction ? ldf(correction + e) : 0.f);
+				if (!taken && c > bv) bv = c, bi = e, bs = sc;
+			}
+			for (int o = 16; o > 0; o >>= 1) {
+				const float ov = __shfl_xor_sync(0xffffffffu, bv, o), os = __shfl_xor_sync(0xffffffffu, bs, o);
+				const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+				if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi, bs = os;
+			}
+			if (lane == 0) sel[(size_t)n * top + k] = bi, wt[(size_t)n * top + k] = bs * scale;
+			__syncwarp();
+		}
+		return;
+	}
 	float first = 0.f, sum = 0.f;
 	for (int k = 0; k < top; ++k) {
 		float bv = -INFINITY;
@@ -1041,15 +1102,272 @@ __global__ void k_seq_moe_gather(AT* xp, const AT* h, const int* perm, int top, 
 	const size_t r = i / width, c = i % width;
 	xp[i] = h[(size_t)(perm[r] / top) * width + c];
 }
-// x[n] += (res ? res[n] : 0) + sum_k wt[n][k] * y[inv[n * top + k]]   (choices in order of rank)
-__global__ void k_seq_moe_combine(float* x, const float* res, const float* y, const int* inv, const float* wt, int top, int N, int width) {
+// x[n] += (res ? res[n] : 0) + sum_k wt[n][k] * y[inv[n * top + k]]   (choices in order of rank; `store`: x[n] = the sum alone)
+// A choice sel >= real is an identity expert: its output is the token's own input row h[n].
+template <typename AT>
+__global__ void k_seq_moe_combine(float* x, const float* res, const float* y, const int* inv, const float* wt, int top, int N, int width, const int* sel, int real, const AT* h,
+                                  int store) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
 	if (i >= (size_t)N * width) return;
 	const size_t n = i / width, c = i % width;
 	float s = 0.f;
-	for (int k = 0; k < top; ++k) s = fmaf(wt[n * top + k], y[(size_t)inv[n * top + k] * width + c], s);
-	x[i] += res ? res[i] + s : s;
+	for (int k = 0; k < top; ++k) {
+		const float v = sel[n * top + k] >= real ? ldf(h + i) : y[(size_t)inv[n * top + k] * width + c];
+		s = fmaf(wt[n * top + k], v, s);
+	}
+	if (store) x[i] = s;
+	else x[i] += res ? res[i] + s : s;
+}
+
+// ---------------------------------------------------------------- hyper-connections: several copies of the residual stream
+// x is [N][streams][width].  Read: u = sum_s in[s] x_s (in == null: every stream counts once), then the RMS norm of u with a weight
+// per column (w_len = width) or one number for all (w_len = 1); one CTA per row, rows[] picks tokens (the rows whose logits are wanted).
+template <typename AT>
+__global__ void __launch_bounds__(256) k_seq_hc_read(AT* out, const float* x, const int* rows, const bf16* in, const bf16* w, int w_len, float offset, float eps, int R, int width,
+                                                     int streams) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	__shared__ float red[8];
+	const int tid = threadIdx.x, nt = blockDim.x, r = blockIdx.x;
+	const float* src = x + (size_t)(rows ? rows[r] : r) * streams * width;
+	auto mixed = [&](int c) {
+		float u = 0.f;
+		for (int s = 0; s < streams; ++s) u = fmaf(in ? ldf(in + s) : 1.f, src[(size_t)s * width + c], u);
+		return u;
+	};
+	float keep[RMS_KEEP];
+	float ss = 0.f;
+#pragma unroll
+	for (int i = 0; i < RMS_KEEP; ++i) {
+		const int c = i * nt + tid;
+		keep[i] = c < width ? mixed(c) : 0.f;
+		ss = fmaf(keep[i], keep[i], ss);
+	}
+	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) {
+		const float u = mixed(c);
+		ss = fmaf(u, u, ss);
+	}
+	ss = warp_sum(ss);
+	if ((tid & 31) == 0) red[tid >> 5] = ss;
+	__syncthreads();
+	ss = 0.f;
+	for (int i = 0; i < (nt >> 5); ++i) ss += red[i];
+	const float rinv = 1.f / sqrtf(ss / (float)width + eps);
+	AT* d = out + (size_t)r * width;
+#pragma unroll
+	for (int i = 0; i < RMS_KEEP; ++i) {
+		const int c = i * nt + tid;
+		if (c < width) d[c] = to_act<AT>(keep[i] * rinv * (ldf(w + (w_len == 1 ? 0 : c)) + offset));
+	}
+	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) d[c] = to_act<AT>(mixed(c) * rinv * (ldf(w + (w_len == 1 ? 0 : c)) + offset));
+}
+// Write: x_t <- sum_s mix[s][t] x_s + out[t] y for every stream t at once, from the old streams.  y = base (the sublayer's last product,
+// or null) + the routed experts' weighted sum when `moe` is set (choices in order of rank; identity experts return the input row h).
+#define HC_MAX 16
+struct HcMoe {
+	const float* y;  // [pairs][width] grouped expert outputs, or null: no routed part
+	const int* inv;
+	const int* sel;
+	const float* wt;
+	int top, real;
+};
+template <typename AT>
+__global__ void k_seq_hc_write(float* x, const float* base, const bf16* mix, const bf16* outw, int N, int width, int streams, HcMoe moe, const AT* h) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= (size_t)N * width) return;
+	const size_t n = i / width, c = i % width;
+	float y = base ? base[i] : 0.f;
+	if (moe.y) {
+		float s = 0.f;
+		for (int k = 0; k < moe.top; ++k) {
+			const float v = moe.sel[n * moe.top + k] >= moe.real ? ldf(h + i) : moe.y[(size_t)moe.inv[n * moe.top + k] * width + c];
+			s = fmaf(moe.wt[n * moe.top + k], v, s);
+		}
+		y += s;
+	}
+	float old[HC_MAX];
+	float* xp = x + n * streams * width + c;
+#pragma unroll
+	for (int s = 0; s < HC_MAX; ++s)
+		if (s < streams) old[s] = xp[(size_t)s * width];
+	for (int t = 0; t < streams; ++t) {
+		float v = 0.f;
+#pragma unroll
+		for (int s = 0; s < HC_MAX; ++s)
+			if (s < streams) v = fmaf(ldf(mix + s * streams + t), old[s], v);
+		xp[(size_t)t * width] = fmaf(ldf(outw + t), y, v);
+	}
+}
+// out[n] = sum of the streams of token n
+__global__ void k_seq_stream_sum(float* out, const float* x, int N, int width, int streams) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= (size_t)N * width) return;
+	const size_t n = i / width, c = i % width;
+	float v = 0.f;
+	for (int s = 0; s < streams; ++s) v += x[(n * streams + s) * width + c];
+	out[i] = v;
+}
+
+// ---------------------------------------------------------------- linear recurrences served by the gated-linear-attention scan
+// mLSTM, HGRN2 and Mamba-2 are all S <- diag(a) S + k v^T, o = S^T q per head; what differs is how a, k, v, q come out of the
+// projection and what happens to o.  A preparation kernel writes them as the scan's input (`lin`: rows [q | k | v] per token, and
+// the decay matrix), the scan itself is k_seq_gla_scan, k_seq_lin_out finishes.
+
+// mLSTM gates.  Per (sequence, head), over the step's tokens in order, with the running maximum m carried in the slot state:
+//   li = cap tanh((i_raw) / cap), lf = logsigmoid(cap tanh(f_raw / cap)), m_t = max(lf + m_(t-1), li),
+//   keep_t = exp(lf + m_(t-1) - m_t), take_t = exp(li - m_t).
+// One warp per (sequence, head), 32 tokens per round: with F the running sum of lf inside the round, m_t = F_t + max(m_in, max_(s<=t)(li_s - F_s)).
+struct MlstmGates {
+	const float* proj; // biased projection; raw gates at columns icol + h, fcol + h
+	int ldp, icol, fcol, heads;
+	float cap;
+	float* m_state;    // [slots][heads]
+	float* keep;       // [N][heads]
+	float* take;       // [N][heads]
+	float* m_out;      // [N][heads]
+};
+__global__ void k_seq_mlstm_gates(MlstmGates a, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+	const int start = sb.sstart[b], cnt = sb.scount[b];
+	float* mp = a.m_state + (size_t)sb.sslot[b] * a.heads + h;
+	float m_in = *mp;
+	for (int t0 = 0; t0 < cnt; t0 += 32) {
+		const int t = t0 + lane;
+		const bool live = t < cnt;
+		float li = -INFINITY, lf = 0.f;
+		if (live) {
+			const float* pr = a.proj + (size_t)(start + t) * a.ldp;
+			li = a.cap * tanhf(pr[a.icol + h] / a.cap);
+			const float fr = a.cap * tanhf(pr[a.fcol + h] / a.cap);
+			lf = -softplusf_(-fr);
+		}
+		float F = lf;
+		for (int o = 1; o < 32; o <<= 1) {
+			const float up = __shfl_up_sync(0xffffffffu, F, o);
+			if (lane >= o) F += up;
+		}
+		float A = li - F;
+		for (int o = 1; o < 32; o <<= 1) {
+			const float up = __shfl_up_sync(0xffffffffu, A, o);
+			if (lane >= o) A = fmaxf(A, up);
+		}
+		const float m = F + fmaxf(m_in, A);
+		float m_prev = __shfl_up_sync(0xffffffffu, m, 1);
+		if (lane == 0) m_prev = m_in;
+		if (live) {
+			const size_t o = (size_t)(start + t) * a.heads + h;
+			a.keep[o] = expf(lf + m_prev - m), a.take[o] = expf(li - m), a.m_out[o] = m;
+		}
+		m_in = __shfl_sync(0xffffffffu, m, min(31, cnt - t0 - 1));
+	}
+	if (lane == 0) *mp = m_in;
+}
+
+// Scan input of one token and head.  lin row: [q: heads*dim | k: heads*dim | v: heads*vs], decay row: [heads*dim].
+//   LIN_MLSTM : q, k as projected; v' = take * [v, 1, 0..] (vs = vdim rounded up past one extra column: the normaliser n rides as a value
+//               column of ones); decay = keep for every channel.
+//   LIN_HGRN2 : q = silu(q_raw); f = l + (1 - l) sigmoid(f_raw); k = 1 - f; decay = f; v as projected.
+//   LIN_MAMBA2: q = C and k = B of the head's group (after the convolution); dt = softplus(dt_raw + dt_bias); v' = dt x; decay = exp(-exp(A_log) dt).
+enum { LIN_MLSTM = 0, LIN_HGRN2 = 1, LIN_MAMBA2 = 2 };
+struct LinPack {
+	int mode;
+	const float* proj;
+	int ldp, qcol, kcol, vcol; // HGRN2: kcol = the raw forget gate's column
+	const float *keep, *take;  // LIN_MLSTM
+	const bf16* lower;         // LIN_HGRN2
+	const float *xs, *bs, *cs; // LIN_MAMBA2: convolved x [N][heads*vdim], B and C [N][groups*dim]
+	int dtcol, groups;
+	const bf16 *dt_bias, *a_log;
+	float* lin;
+	float* decay;
+	int heads, dim, vdim, vs;
+};
+__global__ void k_seq_lin_pack(LinPack a, int N) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const int n = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, H = a.heads, D = a.dim, V = a.vdim;
+	const int ldl = 2 * H * D + H * a.vs;
+	const float* pr = a.proj + (size_t)n * a.ldp;
+	float* lq = a.lin + (size_t)n * ldl + h * D;
+	float* lk = lq + H * D;
+	float* lv = a.lin + (size_t)n * ldl + 2 * H * D + h * a.vs;
+	float* dc = a.decay + ((size_t)n * H + h) * D;
+	if (a.mode == LIN_MLSTM) {
+		const float keep = a.keep[(size_t)n * H + h], take = a.take[(size_t)n * H + h];
+		for (int i = tid; i < D; i += blockDim.x) lq[i] = pr[a.qcol + h * D + i], lk[i] = pr[a.kcol + h * D + i], dc[i] = keep;
+		for (int i = tid; i < a.vs; i += blockDim.x) lv[i] = i < V ? take * pr[a.vcol + h * V + i] : i == V ? take : 0.f;
+	} else if (a.mode == LIN_HGRN2) {
+		for (int i = tid; i < D; i += blockDim.x) {
+			const float q = pr[a.qcol + h * D + i], l = ldf(a.lower + h * D + i);
+			const float f = l + (1.f - l) * sigmoidf_(pr[a.kcol + h * D + i]);
+			lq[i] = q * sigmoidf_(q), lk[i] = 1.f - f, dc[i] = f;
+		}
+		for (int i = tid; i < a.vs; i += blockDim.x) lv[i] = i < V ? pr[a.vcol + h * V + i] : 0.f;
+	} else {
+		const int g = h / (H / a.groups);
+		const float dt = softplusf_(pr[a.dtcol + h] + ldf(a.dt_bias + h));
+		const float dec = expf(-expf(ldf(a.a_log + h)) * dt);
+		for (int i = tid; i < D; i += blockDim.x) {
+			lq[i] = a.cs[((size_t)n * a.groups + g) * D + i], lk[i] = a.bs[((size_t)n * a.groups + g) * D + i], dc[i] = dec;
+		}
+		for (int i = tid; i < a.vs; i += blockDim.x) lv[i] = i < V ? dt * a.xs[((size_t)n * H + h) * V + i] : 0.f;
+	}
+}
+
+// Read-out of a linear recurrence.  The token's heads*vdim outputs (o[n*ldo + h*ohs + d]) are taken in units of `unit` columns (vdim: per
+// head; heads*vdim / groups: equal parts); one warp per (token, unit):
+//   mLSTM (m_t given): o /= max(|o[.., vdim]|, exp(-m_t)) + 1e-6 first (column vdim of the head holds n . q);
+//   skip given: o += skip_w[h] * skip[n][h*vdim + d];   gate_mode 3: o *= silu(gate) BEFORE the norm;
+//   then RMS over the unit (eps inside the root), times w[col % w_mod] (null: no weight), times sigmoid(gate) (gate_mode 1), times mul.
+struct LinOut {
+	const float* o;
+	int ldo, ohs, heads, vdim, unit;
+	const bf16* w;
+	int w_mod;
+	const float* gate;
+	int ldg, gate_mode;
+	const float* m_t;     // [N][heads] or null
+	const float* skip;    // [N][heads*vdim] or null
+	const bf16* skip_w;   // [heads]
+	float eps, mul;
+};
+template <typename AT>
+__global__ void k_seq_lin_out(AT* out, LinOut a, int N) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int inner = a.heads * a.vdim, units = inner / a.unit;
+	const size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + warp;
+	if (u >= (size_t)N * units) return;
+	const size_t n = u / units;
+	const int c0 = (int)(u % units) * a.unit;
+	auto value = [&](int c) {
+		const int h = c / a.vdim, d = c % a.vdim;
+		const float* oh = a.o + n * a.ldo + (size_t)h * a.ohs;
+		float v = oh[d];
+		if (a.m_t) v /= fmaxf(fabsf(oh[a.vdim]), expf(-a.m_t[n * a.heads + h])) + 1e-6f;
+		if (a.skip) v = fmaf(ldf(a.skip_w + h), a.skip[n * inner + c], v);
+		if (a.gate_mode == 3) {
+			const float g = a.gate[n * a.ldg + c];
+			v *= g * sigmoidf_(g);
+		}
+		return v;
+	};
+	float ss = 0.f;
+	for (int i = lane; i < a.unit; i += 32) {
+		const float v = value(c0 + i);
+		ss = fmaf(v, v, ss);
+	}
+	ss = warp_sum(ss);
+	const float r = 1.f / sqrtf(ss / (float)a.unit + a.eps) * a.mul;
+	for (int i = lane; i < a.unit; i += 32) {
+		const int c = c0 + i;
+		float v = value(c) * r;
+		if (a.w) v *= ldf(a.w + c % a.w_mod);
+		if (a.gate_mode == 1) v *= sigmoidf_(a.gate[n * a.ldg + c]);
+		out[n * inner + c] = to_act<AT>(v);
+	}
 }
 
 // ---------------------------------------------------------------- products  Y[n][m] = sum_k X[n][k] W[m][k]
@@ -1078,6 +1396,7 @@ struct GemmArgs {
 	int split;               // > 0: output columns m >= split leave as relu(acc)^2 in the activation type to Y2[n][m - split] (row stride ldy2), whatever epi says
 	void* Y2;
 	long ldy2;
+	float out_scale = 0.f;   // != 0: the accumulator (after the bias) is multiplied by it
 };
 // rows of batch z: first row and count
 struct GemmRows {
@@ -1093,6 +1412,7 @@ __device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, const GemmR
 	if (n >= gr.count || m >= a.M) return;
 	const size_t o = (size_t)z * a.ybs + (size_t)(gr.base + n) * a.ldy + m;
 	if (a.bias) acc += ldf(a.bias + (size_t)z * a.M + m);
+	if (a.out_scale != 0.f) acc *= a.out_scale;
 	if (a.split > 0 && m >= a.split) {
 		const float r = fmaxf(acc, 0.f);
 		((AT*)a.Y2)[(size_t)(gr.base + n) * a.ldy2 + (m - a.split)] = to_act<AT>(r * r);

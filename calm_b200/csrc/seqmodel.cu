@@ -8,6 +8,8 @@
 #include <string.h>
 
 #include <algorithm>
+#include <array>
+#include <functional>
 #include <map>
 #include <type_traits>
 #include <vector>
@@ -19,9 +21,9 @@ namespace {
 
 uint64_t g_seq_launches = 0;
 
-enum Kind { KD_EMBED, KD_NORM, KD_GEMM, KD_GEMM_TC, KD_GEMM_SKINNY, KD_CONV, KD_ATTN_LATENT, KD_ATTN_WINDOW, KD_DELTA, KD_ELEMENT, KD_QK, KD_GLA, KD_ROUTE, KD_COUNT };
+enum Kind { KD_EMBED, KD_NORM, KD_GEMM, KD_GEMM_TC, KD_GEMM_SKINNY, KD_CONV, KD_ATTN_LATENT, KD_ATTN_WINDOW, KD_DELTA, KD_ELEMENT, KD_QK, KD_GLA, KD_ROUTE, KD_HYPER, KD_LINPREP, KD_COUNT };
 const char* const kKindNames[KD_COUNT] = {"embed", "norm", "gemm", "gemm_tcgen05", "gemm_skinny", "conv", "attention_latent", "attention_window", "delta_scan", "elementwise",
-                                          "qk_prep", "gla_scan", "moe_route"};
+                                          "qk_prep", "gla_scan", "moe_route", "hyper", "lin_prep"};
 
 // what one run of a layer owns (a looped layer has one of these per pass)
 struct RunState {
@@ -32,6 +34,10 @@ struct RunState {
 	float* conv = nullptr;    // [slots][taps-1][channels]
 	float* delta = nullptr;   // SEQ_DELTA / SEQ_GLA: the recurrent state [slots][heads][dim][vdim]
 	size_t conv_per_slot = 0, delta_per_slot = 0;
+	float* mstate = nullptr;  // SEQ_MLSTM: the running maximum of the log gates [slots][heads]
+	size_t m_per_slot = 0;
+	float* slopes = nullptr;  // SEQ_GQA with dist_bias: the penalty per position of distance, per head
+	std::vector<RunState> sub; // SEQ_PAIR: the two mixers' own caches and state
 };
 
 struct Slot {
@@ -43,6 +49,7 @@ struct Slot {
 struct Seq {
 	SeqModel m;
 	std::vector<SeqLayer> layers;
+	std::vector<std::array<SeqLayer, 2>> pairs;
 	std::vector<RunState> runs;
 	std::vector<double*> rot_freq; // per layer: angle step of every rotated pair (SEQ_GQA), device
 	std::vector<float> rot_mag;    // per layer: factor on cos and sin
@@ -67,7 +74,10 @@ struct Seq {
 	float *x = nullptr, *x0 = nullptr, *proj = nullptr, *f[6] = {};
 	void* ah = nullptr;                               // parallel blocks: a dense unit's hidden activations, written by the mixer's input product
 	size_t w_ah = 0;
-	float* mo = nullptr;                              // parallel blocks: the mixer's output until the feed-forward's is added with it
+	float* mo = nullptr;                              // parallel blocks: the mixer's output until the feed-forward's is added with it; hyper blocks: a sublayer's output
+	float* lin = nullptr;                             // scan input of the linear recurrences served by the gated-linear-attention scan: rows [q | k | v]
+	size_t w_lin = 0;
+	int streams = 1;
 	// routed experts: choices and weights per token, groups, and the grouped activations of max_top choices per token
 	int max_top = 0, max_experts = 0;
 	size_t w_moe_ff = 0;
@@ -147,7 +157,11 @@ size_t in_rows(const SeqLayer& L) {
 	switch (L.type) {
 	case SEQ_LATENT: return (size_t)L.q_rank + L.kv_rank + L.heads;
 	case SEQ_DELTA: return (size_t)2 * L.kv_heads * L.dim + (size_t)L.heads * L.vdim + L.heads + L.a_rank + L.g_rank;
-	case SEQ_GQA: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim + (size_t)L.heads * L.vdim;
+	case SEQ_GQA: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim + (L.no_gate ? 0 : (size_t)L.heads * L.vdim);
+	case SEQ_MLSTM: return (size_t)2 * L.heads * L.dim + (size_t)2 * L.heads * L.vdim + 2 * L.heads;
+	case SEQ_HGRN2: return (size_t)2 * L.heads * L.dim + (size_t)L.heads * L.vdim;
+	case SEQ_MAMBA2: return (size_t)2 * L.heads * L.vdim + (size_t)2 * L.kv_heads * L.dim + L.heads;
+	case SEQ_PAIR: return 0;
 	case SEQ_GLA: return (size_t)2 * L.heads * L.dim + (size_t)2 * L.heads * L.vdim + L.a_rank;
 	default: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim;
 	}
@@ -160,8 +174,12 @@ int proj_stride(const SeqLayer& L) {
 int conv_channels(const SeqLayer& L) {
 	if (L.type == SEQ_DELTA) return 2 * L.kv_heads * L.dim + L.heads * L.vdim;
 	if (L.type == SEQ_WINDOW) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim;
+	if (L.type == SEQ_MAMBA2) return L.heads * L.vdim + 2 * L.kv_heads * L.dim;
 	return 0;
 }
+// value columns of a linear recurrence's scan: the mLSTM carries its normaliser as one more column; whole float4s either way
+int lin_vs(const SeqLayer& L) { return ((L.type == SEQ_MLSTM ? L.vdim + 1 : L.vdim) + 3) & ~3; }
+bool is_lin(const SeqLayer& L) { return L.type == SEQ_MLSTM || L.type == SEQ_HGRN2 || L.type == SEQ_MAMBA2; }
 // gated linear attention: key channels per lane when `lanes` lanes share a value column, the scan's shared memory, the row length
 // of a value column in the state (the same whichever lane count a step runs with), and the kernel's instantiations
 int gla_rows(int dim, int lanes) {
@@ -196,15 +214,24 @@ int attn_tile(int group, int kd, int vd) {
 }
 size_t attn_smem(int tile, int kd) { return ((size_t)tile * (kd + ATT_KC + 3) + 4) * sizeof(float); }
 
-void validate(const Seq& s) {
+void validate_mixer(const Seq& s, int i, const SeqLayer& L, bool inner) {
 	const SeqModel& m = s.m;
-	if (m.vocab < 1 || m.width < 1 || m.n_layers < 1) CALM_FATAL("seq: empty model");
-	if (m.page < 1 || m.max_seqs < 1 || m.max_tokens < 1) CALM_FATAL("seq: page, max_seqs and max_tokens must be positive");
-	if (m.loop_times > 1 && !(0 <= m.loop_start && m.loop_start < m.loop_stop && m.loop_stop <= m.n_layers)) CALM_FATAL("seq: bad loop span");
-	for (int i = 0; i < m.n_layers; ++i) {
-		const SeqLayer& L = s.layers[i];
+	{
+		if (L.type == SEQ_PAIR) {
+			if (inner || !L.pair) CALM_FATAL("seq: layer %d: a pair holds two plain mixers", i);
+			validate_mixer(s, i, L.pair[0], true), validate_mixer(s, i, L.pair[1], true);
+			return;
+		}
 		if (L.heads < 1 || L.dim < 1 || L.vdim < 1) CALM_FATAL("seq: layer %d: heads, dim and vdim must be positive", i);
-		if (L.type == SEQ_LATENT) {
+		if (is_lin(L)) {
+			if (L.dim > 256) CALM_FATAL("seq: layer %d: a linear-recurrence head holds at most 256 key channels", i);
+			if (L.type == SEQ_MLSTM && !(L.gate_cap > 0.f)) CALM_FATAL("seq: layer %d: gate_cap must be positive", i);
+			if (L.type == SEQ_MAMBA2) {
+				if (L.kv_heads < 1 || L.heads % L.kv_heads) CALM_FATAL("seq: layer %d: heads must be a multiple of the groups", i);
+				if (L.norm_groups < 1 || (L.heads * L.vdim) % L.norm_groups) CALM_FATAL("seq: layer %d: norm_groups must divide heads * vdim", i);
+				if (L.taps < 1) CALM_FATAL("seq: layer %d: taps must be positive", i);
+			}
+		} else if (L.type == SEQ_LATENT) {
 			if (L.q_rank < 1 || L.kv_rank < 1) CALM_FATAL("seq: layer %d: latent ranks must be positive", i);
 			if (cdiv(L.kv_rank, ATT_THREADS) > ATT_MAXI) CALM_FATAL("seq: layer %d: kv_rank %d is more than the attention kernel holds", i, L.kv_rank);
 		} else if (L.type == SEQ_DELTA || L.type == SEQ_WINDOW) {
@@ -227,18 +254,41 @@ void validate(const Seq& s) {
 			if (L.a_rank < 1) CALM_FATAL("seq: layer %d: the decay rank must be positive", i);
 			if (!(L.tau > 0.f)) CALM_FATAL("seq: layer %d: tau must be positive", i);
 		} else CALM_FATAL("seq: layer %d: unknown mixer %d", i, L.type);
+		if ((L.type != SEQ_GQA && (L.chunk || L.dist_bias || L.add_one || L.v_norm || L.no_gate)) || L.chunk < 0) CALM_FATAL("seq: layer %d: chunk, dist_bias, add_one, v_norm and no_gate are options of SEQ_GQA", i);
+		(void)m;
+	}
+}
+
+void validate(const Seq& s) {
+	const SeqModel& m = s.m;
+	if (m.vocab < 1 || m.width < 1 || m.n_layers < 1) CALM_FATAL("seq: empty model");
+	if (m.page < 1 || m.max_seqs < 1 || m.max_tokens < 1) CALM_FATAL("seq: page, max_seqs and max_tokens must be positive");
+	if (m.loop_times > 1 && !(0 <= m.loop_start && m.loop_start < m.loop_stop && m.loop_stop <= m.n_layers)) CALM_FATAL("seq: bad loop span");
+	if (m.streams < 0 || m.streams > HC_MAX) CALM_FATAL("seq: at most %d streams", HC_MAX);
+	if (m.block != SEQ_BLOCK_HYPER && m.streams > 1) CALM_FATAL("seq: several streams need hyper blocks");
+	if (m.block == SEQ_BLOCK_HYPER && m.loop_times > 1) CALM_FATAL("seq: hyper blocks are not served inside a looped span");
+	if (m.pos_table && m.max_positions < 1) CALM_FATAL("seq: a position table needs max_positions");
+	for (int i = 0; i < m.n_layers; ++i) {
+		const SeqLayer& L = s.layers[i];
+		validate_mixer(s, i, L, false);
+		if (m.block == SEQ_BLOCK_HYPER && (!L.hc1.in || !L.hc1.out || !L.hc1.mix || (L.ff > 0 && (!L.hc2.in || !L.hc2.out || !L.hc2.mix))))
+			CALM_FATAL("seq: layer %d: hyper blocks need in, out and mix of every sublayer", i);
+		if (m.block != SEQ_BLOCK_HYPER && (L.type == SEQ_PAIR || is_lin(L))) CALM_FATAL("seq: layer %d: this mixer is served in hyper blocks", i);
 		if (L.ff > 0) {
 			if (L.ff_kind < SEQ_FF_CLAMPED || L.ff_kind > SEQ_FF_MOE) CALM_FATAL("seq: layer %d: unknown feed-forward kind %d", i, L.ff_kind);
 			if (L.in_tail != 0 && (m.block != SEQ_BLOCK_PARALLEL || L.in_tail != (L.ff_kind == SEQ_FF_MOE ? L.experts : L.ff_kind == SEQ_FF_RELU2 ? L.ff : -1)))
 				CALM_FATAL("seq: layer %d: in_tail must be the router's or the up projection's row count, in a parallel block", i);
 			if (L.ff_kind == SEQ_FF_MOE) {
-				if (L.experts < 1 || L.top < 1 || L.top > L.experts) CALM_FATAL("seq: layer %d: 1 <= top <= experts", i);
-				if (m.block != SEQ_BLOCK_PARALLEL) CALM_FATAL("seq: layer %d: routed experts are served in parallel blocks only", i);
+				if (L.experts < 1 || L.top < 1 || L.top > L.experts + L.ident) CALM_FATAL("seq: layer %d: 1 <= top <= experts", i);
+				if (m.block == SEQ_BLOCK_SERIAL) CALM_FATAL("seq: layer %d: routed experts are not served in serial blocks", i);
+				if (L.ident < 0 || L.top > L.experts + L.ident || L.shared_ff < 0) CALM_FATAL("seq: layer %d: bad identity experts or shared unit", i);
+				if (m.block != SEQ_BLOCK_HYPER && (L.ident || L.shared_ff || L.route_mode)) CALM_FATAL("seq: layer %d: identity experts, the shared unit and route_mode 1 are served in hyper blocks", i);
 			}
 		}
 	}
 	if (m.norm_kind != SEQ_NORM_DYT && m.norm_kind != SEQ_NORM_RMS) CALM_FATAL("seq: unknown norm kind %d", m.norm_kind);
-	if (m.block != SEQ_BLOCK_SERIAL && m.block != SEQ_BLOCK_PARALLEL) CALM_FATAL("seq: unknown block form %d", m.block);
+	if (m.block != SEQ_BLOCK_SERIAL && m.block != SEQ_BLOCK_PARALLEL && m.block != SEQ_BLOCK_HYPER) CALM_FATAL("seq: unknown block form %d", m.block);
+	if (m.block == SEQ_BLOCK_HYPER && m.norm_kind != SEQ_NORM_RMS) CALM_FATAL("seq: hyper blocks use the RMS norm");
 	if (m.block == SEQ_BLOCK_SERIAL && m.norm_kind != SEQ_NORM_DYT)
 		CALM_FATAL("seq: serial blocks fold their second norm into the product before it, which only a norm without row statistics (Dynamic Tanh) allows");
 }
@@ -272,7 +322,8 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 		const size_t cn = N;
 		cudaFree(s.x), cudaFree(s.x0), cudaFree(s.proj), cudaFree(s.hA), cudaFree(s.a1), cudaFree(s.a2), cudaFree(s.a3), cudaFree(s.mo);
 		for (float*& p : s.f) cudaFree(p);
-		if (s.m.block == SEQ_BLOCK_PARALLEL) s.mo = (float*)dalloc(cn * s.m.width * sizeof(float));
+		if (s.m.block != SEQ_BLOCK_SERIAL) s.mo = (float*)dalloc(cn * s.m.width * sizeof(float));
+		if (s.w_lin) cudaFree(s.lin), s.lin = (float*)dalloc(cn * s.w_lin * sizeof(float));
 		if (s.w_ah) cudaFree(s.ah), s.ah = dalloc(cn * s.w_ah * act_size(s));
 		if (s.max_top > 0) {
 			cudaFree(s.moe_sel), cudaFree(s.moe_wt), cudaFree(s.moe_y), cudaFree(s.moe_d), cudaFree(s.moe_x), cudaFree(s.moe_a);
@@ -285,7 +336,7 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 			s.moe_x = dalloc(pairs * s.m.width * act_size(s));
 			s.moe_a = dalloc(pairs * s.w_moe_ff * act_size(s));
 		}
-		s.x = (float*)dalloc(cn * s.m.width * sizeof(float));
+		s.x = (float*)dalloc(cn * s.streams * s.m.width * sizeof(float));
 		s.x0 = (float*)dalloc(cn * s.m.width * sizeof(float));
 		s.proj = (float*)dalloc(cn * s.w_proj * sizeof(float));
 		for (float*& p : s.f) p = (float*)dalloc(cn * s.w_f * sizeof(float));
@@ -313,6 +364,7 @@ struct GemmExtra {
 	const int* seg = nullptr;    // grouped product: rows of batch z
 	int x_rows = 0;              // grouped product: rows of X / Y over all groups
 	float epi_f = 0.f;           // EPI_DECAY: exponent
+	float out_scale = 0.f;       // != 0: factor on the accumulator
 	int split = 0;               // columns from here on leave as relu(.)^2 in the activation type to Y2
 	void* Y2 = nullptr;
 	long ldy2 = 0;
@@ -322,7 +374,7 @@ void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, lo
 	GemmArgs a;
 	const GemmExtra none;
 	if (!ex) ex = &none;
-	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows, a.epi_f = ex->epi_f, a.split = ex->split, a.Y2 = ex->Y2, a.ldy2 = ex->ldy2;
+	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows, a.epi_f = ex->epi_f, a.split = ex->split, a.Y2 = ex->Y2, a.ldy2 = ex->ldy2, a.out_scale = ex->out_scale;
 	a.w_immutable = w_immutable;
 	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
 	a.N = N, a.M = M, a.K = K, a.epi = epi;
@@ -379,6 +431,22 @@ void dyt(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, 
 	});
 }
 
+// most keys a query of this attention sees (0: all earlier positions)
+int attn_span(const SeqLayer& L) {
+	if (L.type == SEQ_LATENT) return 0;
+	int span = L.window > 0 ? L.window + (L.type == SEQ_GQA ? L.keep_first : 0) : 0;
+	if (L.type == SEQ_GQA && L.chunk > 0) span = span > 0 ? std::min(span, L.chunk) : L.chunk;
+	return span;
+}
+// hyper blocks: the weighted sum of the streams (in == null: their plain sum) under the model's RMS norm
+void hc_read(Seq& s, void* out, const int* rows, const void* in, const SeqNorm& nm, int R) {
+	const int W = s.m.width, S = s.streams, wl = s.m.norm_scalar ? 1 : W;
+	run_kernel(s, KD_HYPER, (double)R * W * (4.0 * S + act_size(s)), 0, [&] {
+		const int threads = std::min(256, std::max(32, cdiv(W, 4 * 32) * 32));
+		if (s.m.exact) launch_k(s, k_seq_hc_read<float>, R, threads, 0, (float*)out, s.x, rows, (const bf16*)in, (const bf16*)nm.w, wl, s.m.norm_offset, s.m.eps, R, W, S);
+		else launch_k(s, k_seq_hc_read<bf16>, R, threads, 0, (bf16*)out, s.x, rows, (const bf16*)in, (const bf16*)nm.w, wl, s.m.norm_offset, s.m.eps, R, W, S);
+	});
+}
 // CTAs that share the keys of one (token, head tile): few tokens over a long context
 int attn_nsplit(const Seq& s, int live_tokens, int tiles, int window, int longest) {
 	const int ctas = live_tokens * tiles, chunks = cdiv(window > 0 ? std::min(longest, window) : longest, ATT_KC);
@@ -413,9 +481,12 @@ void attention_products(Seq& s, int kind, const AttArgs& a, bf16* out, const Seq
 	for (int t0 = 0; t0 < count;) {
 		const int q0 = pos0 + t0;
 		int Tb = count - t0;
+		if (a.chunk > 0) Tb = std::min(Tb, (q0 / a.chunk + std::max(1, 256 / a.chunk)) * a.chunk - q0); // a block of queries ends where a block of positions does
 		while (Tb > 64 && (size_t)a.group * Tb * (size_t)(q0 + Tb) > budget) Tb = (Tb + 1) / 2;
 		// gathered keys: the kept first positions the block's window has left behind, then everything from the first query's window on
-		const int k0 = a.window > 0 ? std::max(0, q0 - a.window + 1) : 0, kfb = a.window > 0 ? std::min(a.keep_first, k0) : 0;
+		int k0 = a.window > 0 ? std::max(0, q0 - a.window + 1) : 0;
+		if (a.chunk > 0) k0 = std::max(k0, q0 / a.chunk * a.chunk); // the first query's block; later rows mask what lies before theirs
+		const int kfb = a.window > 0 ? std::min(a.keep_first, k0) : 0;
 		const int C = kfb + q0 + Tb - k0, Cp = (C + 7) & ~7;
 		reserve_attn(s, (size_t)C * a.kd, (size_t)a.vd * Cp, (size_t)a.group * Tb * Cp);
 		for (int kvh = 0; kvh < G; ++kvh) {
@@ -429,6 +500,7 @@ void attention_products(Seq& s, int kind, const AttArgs& a, bf16* out, const Seq
 			AttSoftmax sm;
 			sm.S = s.att_s, sm.P = s.att_p, sm.T = Tb, sm.C = C, sm.Cp = Cp, sm.qpos0 = q0, sm.k0 = k0, sm.window = a.window, sm.scale = a.scale;
 			sm.keep_first = a.window > 0 ? a.keep_first : 0, sm.kfb = kfb;
+			sm.chunk = a.chunk, sm.slopes = a.slopes ? a.slopes + h0 : nullptr, sm.add_one = a.add_one;
 			const bool head_gate = a.gate && a.ges == 0; // one gate per head scales the probabilities; a gate per channel goes into the value product's epilogue
 			sm.sink = a.sink ? a.sink + h0 : nullptr, sm.gate = head_gate ? a.gate + (size_t)(first + t0) * a.ldg + h0 : nullptr, sm.ldg = a.ldg;
 			GemmExtra gx;
@@ -456,7 +528,9 @@ void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, doubl
 	const size_t smem = attn_smem(a.tile, a.kd);
 	// few tokens over a long context: the keys of one (token, head tile) are shared out over several CTAs
 	const int live = a.skip ? std::max(1, sb.N - s.tok_on_products) : sb.N; // tokens the fused kernel really serves (the others' CTAs leave at once)
-	a.nsplit = attn_nsplit(s, live, a.heads / a.tile, a.window > 0 ? a.window + a.keep_first : 0, longest);
+	int span = a.window > 0 ? a.window + a.keep_first : 0;
+	if (a.chunk > 0) span = span > 0 ? std::min(span, a.chunk) : a.chunk;
+	a.nsplit = attn_nsplit(s, live, a.heads / a.tile, span, longest);
 	ensure_part(s, (size_t)sb.N * a.heads * a.nsplit * (a.vd + 2));
 	a.part = s.part;
 	const dim3 grid(sb.N, a.heads / a.tile, a.nsplit);
@@ -476,10 +550,11 @@ void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, doubl
 void conv(Seq& s, const SeqLayer& L, RunState& r, ConvArgs& ca, const SeqBatch& sb) {
 	const int units = ca.seg[0].heads + ca.seg[1].heads + ca.seg[2].heads;
 	ca.proj = s.proj, ca.ldp = proj_stride(L), ca.w = (const bf16*)L.conv, ca.taps = L.taps, ca.channels = conv_channels(L), ca.state = r.conv, ca.eps = s.m.eps;
+	ca.bias = (const bf16*)L.conv_b, ca.pcol = L.type == SEQ_MAMBA2 ? L.heads * L.vdim : 0; // Mamba-2: the channels start behind z
 	const double bytes = (double)sb.N * ca.channels * 8;
 	run_kernel(s, KD_CONV, bytes, 0, [&] { launch_k(s, k_seq_conv_heads, dim3(sb.N, cdiv(units, 4)), 128, 0, ca, sb); });
 	if (L.taps > 1)
-		run_kernel(s, KD_CONV, 0, 0, [&] { launch_k(s, k_seq_conv_state, dim3(cdiv(ca.channels, 128), sb.B), 128, 0, r.conv, s.proj, ca.ldp, L.taps, ca.channels, sb); });
+		run_kernel(s, KD_CONV, 0, 0, [&] { launch_k(s, k_seq_conv_state, dim3(cdiv(ca.channels, 128), sb.B), 128, 0, r.conv, s.proj, ca.ldp, L.taps, ca.channels, sb, ca.pcol); });
 }
 
 // how a sublayer's last product lands in the stream: serial blocks apply the Dynamic Tanh norm after the sublayer and add
@@ -490,19 +565,50 @@ struct OutEpi {
 	const SeqNorm* nrm;
 	float* dst;
 	const float* res;
+	float scale = 0.f; // != 0: factor on the product
+	const SeqHyper* hc = nullptr; // hyper blocks: the routed feed-forward writes the streams itself (its weighted sum is formed in that kernel)
 };
+template <typename AT>
+void hc_write(Seq& s, const SeqHyper& hc, const float* base, const HcMoe& moe, int N) {
+	const int W = s.m.width, S = s.streams;
+	run_kernel(s, KD_HYPER, (double)N * W * (8.0 * S + 4 + (moe.y ? 4.0 * moe.top : 0)), 0, [&] {
+		launch_k(s, k_seq_hc_write<AT>, cdiv((long)N * W, 256), 256, 0, s.x, base, (const bf16*)hc.mix, (const bf16*)hc.out, N, W, S, moe, (const AT*)s.hA);
+	});
+}
 template <typename AT>
 void out_product(Seq& s, const AT* X, const void* Wt, int N, int K, const OutEpi& oe) {
 	GemmExtra gx;
-	gx.res = oe.res;
+	gx.res = oe.res, gx.out_scale = oe.scale;
 	gemm(s, X, K, 0, Wt, K, 0, oe.dst, s.m.width, 0, N, s.m.width, K, 1, oe.epi, oe.nrm, -1, true, &gx);
+}
+
+// the gated-linear-attention scan over a step's tokens: S <- diag(decay) S + k v^T, o = S^T q * qscale per (sequence, head); g names
+// the inputs (columns of a matrix with row stride ld), the state and the output
+void gla_launch(Seq& s, GlaArgs& g, const SeqBatch& sb, int ld) {
+	const int N = sb.N, H = g.heads, D = g.dim, Dv = g.vdim;
+	g.ldp = ld;
+	g.vec = D % 4 == 0 && Dv % 4 == 0 && ld % 4 == 0 && g.qcol % 4 == 0 && g.kcol % 4 == 0 && g.vcol % 4 == 0; // 16-byte copies; cudaMalloc aligns the bases
+	g.ldstate = gla_ldstate(D);
+	// lanes per value column: more of them while sequences x heads x columns alone would leave SMs without a CTA
+	int lanes = 4;
+	while (lanes < 16 && (long)sb.B * H * cdiv(Dv * lanes, 128) < s.sms) lanes *= 2;
+	const int R = gla_rows(D, lanes);
+	const dim3 grid(sb.B, H, cdiv(Dv * lanes, 128));
+	const size_t smem = gla_smem(R, lanes);
+	run_kernel(s, KD_GLA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 4.0, [&] {
+		bool done = false;
+		gla_each([&](auto r, auto p) {
+			if (decltype(r)::value == R && decltype(p)::value == lanes) launch_k(s, k_seq_gla_scan<decltype(r)::value, decltype(p)::value>, grid, 128, smem, g, sb), done = true;
+		});
+		if (!done) CALM_FATAL("seq: no gated-linear-attention scan for %d key channels on %d lanes", D, lanes);
+	});
 }
 
 template <typename AT>
 void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest, const OutEpi& oe) {
 	const int N = sb.N, W = s.m.width, P = proj_stride(L);
 	AT *hA = (AT*)s.hA, *a1 = (AT*)s.a1, *a2 = (AT*)s.a2;
-	{
+	if (L.type != SEQ_PAIR) {
 		// one product for everything that reads the normed input: the mixer's rows, and in parallel blocks the router's rows (fp32, behind
 		// the mixer's) or the dense unit's up rows (leaving as relu^2 in the activation type)
 		GemmExtra gx;
@@ -562,12 +668,61 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		QkArgs qa;
 		qa.proj = s.proj, qa.ldp = P, qa.heads = H, qa.kv_heads = G, qa.dim = D, qa.vdim = Dv, qa.qw = (const bf16*)L.q_norm, qa.kw = (const bf16*)L.k_norm, qa.eps = s.m.eps;
 		qa.rot_dims = L.rot_dims, qa.freq = s.rot_freq[r.layer], qa.mag = s.rot_mag[r.layer], qa.q = s.f[0], qa.kc = r.cache_a, qa.vc = r.cache_b;
+		qa.v_norm = L.v_norm;
 		run_kernel(s, KD_QK, (double)N * (H * D + G * D + G * Dv) * 8, 0, [&] { launch_k(s, k_seq_qk_rope, N, 256, (size_t)std::max(L.rot_dims, 1) * sizeof(float), qa, sb); });
 		AttArgs a;
 		a.q = s.f[0], a.kc = r.cache_a, a.vc = r.cache_b, a.kld = G * D, a.vld = G * Dv, a.heads = H, a.group = H / G, a.tile = attn_tile(H / G, D, Dv), a.kd = D, a.vd = Dv;
 		a.window = L.window, a.keep_first = L.window > 0 ? L.keep_first : 0, a.scale = L.scale, a.sink = nullptr;
-		a.gate = s.proj + H * D + G * D + G * Dv, a.ldg = P, a.ghs = Dv, a.ges = 1; // a sigmoid gate per output channel, from the same stacked projection
-		attention(s, KD_ATTN_WINDOW, a, a2, sb, L.window > 0 ? std::min(kv_rows, (double)N * (L.window + L.keep_first)) : kv_rows, longest);
+		a.gate = L.no_gate ? nullptr : s.proj + H * D + G * D + G * Dv, a.ldg = P, a.ghs = Dv, a.ges = 1; // a sigmoid gate per output channel, from the same stacked projection
+		a.chunk = L.chunk, a.slopes = L.dist_bias ? r.slopes : nullptr, a.add_one = L.add_one;
+		const int span = attn_span(L);
+		attention(s, KD_ATTN_WINDOW, a, a2, sb, span > 0 ? std::min(kv_rows, (double)N * span) : kv_rows, longest);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+	} else if (L.type == SEQ_PAIR) {
+		// two mixers on the same normed input: the first one's product lands scaled in the destination, the second one's is added scaled
+		if (oe.epi != EPI_F32) CALM_FATAL("seq: a pair writes its sum to a buffer of its own");
+		OutEpi first = oe, second = oe;
+		first.scale = L.pair_scale[0], second.epi = EPI_RES, second.res = nullptr, second.scale = L.pair_scale[1];
+		mixer_typed<AT>(s, L.pair[0], r.sub[0], sb, kv_rows, longest, first);
+		mixer_typed<AT>(s, L.pair[1], r.sub[1], sb, kv_rows, longest, second);
+	} else if (is_lin(L)) {
+		// mLSTM, HGRN2, Mamba-2: gates and inputs are prepared in fp32, the recurrence is the gated-linear-attention scan, a read-out kernel finishes
+		const int H = L.heads, D = L.dim, Dv = L.vdim, Vs = lin_vs(L), ldl = 2 * H * D + H * Vs;
+		LinPack lp;
+		memset(&lp, 0, sizeof(lp));
+		lp.proj = s.proj, lp.ldp = P, lp.lin = s.lin, lp.decay = s.f[3], lp.heads = H, lp.dim = D, lp.vdim = Dv, lp.vs = Vs;
+		LinOut lo;
+		memset(&lo, 0, sizeof(lo));
+		lo.o = s.f[5], lo.ldo = H * Vs, lo.ohs = Vs, lo.heads = H, lo.vdim = Dv, lo.unit = Dv, lo.w = (const bf16*)L.out_norm, lo.eps = s.m.eps, lo.mul = 1.f;
+		float qscale = 1.f;
+		if (L.type == SEQ_MLSTM) {
+			const int cq = 0, ck = H * D, cv = 2 * H * D, cg = cv + H * Dv, ci = cg + H * Dv, cf = ci + H;
+			MlstmGates mg{s.proj, P, ci, cf, H, L.gate_cap, r.mstate, s.f[0], s.f[1], s.f[2]};
+			run_kernel(s, KD_LINPREP, (double)N * H * 20, 0, [&] { launch_k(s, k_seq_mlstm_gates, dim3(sb.B, H), 32, 0, mg, sb); });
+			lp.mode = LIN_MLSTM, lp.qcol = cq, lp.kcol = ck, lp.vcol = cv, lp.keep = s.f[0], lp.take = s.f[1];
+			lo.w_mod = H * Dv, lo.gate = s.proj + cg, lo.ldg = P, lo.gate_mode = 1, lo.m_t = s.f[2];
+			qscale = 1.f / sqrtf((float)D);
+		} else if (L.type == SEQ_HGRN2) {
+			lp.mode = LIN_HGRN2, lp.qcol = 0, lp.kcol = H * D, lp.vcol = 2 * H * D, lp.lower = (const bf16*)L.lower;
+			lo.w_mod = Dv;
+		} else {
+			const int G = L.kv_heads, inner = H * Dv;
+			ConvArgs ca;
+			ca.seg[0] = ConvSeg{0, H, Dv, 1, 0, 1.f, 0, s.f[0]};
+			ca.seg[1] = ConvSeg{inner, G, D, 1, 0, 1.f, 0, s.f[1]};
+			ca.seg[2] = ConvSeg{inner + G * D, G, D, 1, 0, 1.f, 0, s.f[2]};
+			conv(s, L, r, ca, sb);
+			lp.mode = LIN_MAMBA2, lp.xs = s.f[0], lp.bs = s.f[1], lp.cs = s.f[2], lp.dtcol = 2 * inner + 2 * G * D, lp.groups = G;
+			lp.dt_bias = (const bf16*)L.dt_bias, lp.a_log = (const bf16*)L.a_log;
+			lo.unit = inner / L.norm_groups, lo.w_mod = inner, lo.gate = s.proj, lo.ldg = P, lo.gate_mode = 3, lo.skip = s.f[0], lo.skip_w = (const bf16*)L.skip_d;
+		}
+		run_kernel(s, KD_LINPREP, (double)N * (ldl + H * D) * 8, 0, [&] { launch_k(s, k_seq_lin_pack, dim3(N, H), 64, 0, lp, N); });
+		GlaArgs g;
+		g.proj = s.lin, g.qcol = 0, g.kcol = H * D, g.vcol = 2 * H * D, g.decay = s.f[3], g.qscale = qscale;
+		g.state = r.delta, g.o = s.f[5], g.heads = H, g.dim = D, g.vdim = Vs;
+		gla_launch(s, g, sb, ldl);
+		const long units = (long)N * (H * Dv / lo.unit);
+		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0, [&] { launch_k(s, k_seq_lin_out<AT>, cdiv(units, 4), 128, 0, a2, lo, N); });
 		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
 	} else if (L.type == SEQ_GLA) {
 		const int H = L.heads, D = L.dim, Dv = L.vdim;
@@ -581,21 +736,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		GlaArgs g;
 		g.proj = s.proj, g.ldp = P, g.qcol = cq, g.kcol = ck, g.vcol = cv, g.decay = s.f[3], g.qscale = 1.f / sqrtf((float)D);
 		g.state = r.delta, g.o = s.f[5], g.heads = H, g.dim = D, g.vdim = Dv;
-		g.vec = D % 4 == 0 && Dv % 4 == 0 && P % 4 == 0; // column offsets are then multiples of 4 as well, and cudaMalloc aligns the bases
-		g.ldstate = gla_ldstate(D);
-		// lanes per value column: more of them while sequences x heads x columns alone would leave SMs without a CTA
-		int lanes = 4;
-		while (lanes < 16 && (long)sb.B * H * cdiv(Dv * lanes, 128) < s.sms) lanes *= 2;
-		const int R = gla_rows(D, lanes);
-		const dim3 grid(sb.B, H, cdiv(Dv * lanes, 128));
-		const size_t smem = gla_smem(R, lanes);
-		run_kernel(s, KD_GLA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 4.0, [&] {
-			bool done = false;
-			gla_each([&](auto r, auto p) {
-				if (decltype(r)::value == R && decltype(p)::value == lanes) launch_k(s, k_seq_gla_scan<decltype(r)::value, decltype(p)::value>, grid, 128, smem, g, sb), done = true;
-			});
-			if (!done) CALM_FATAL("seq: no gated-linear-attention scan for %d key channels on %d lanes", D, lanes);
-		});
+		gla_launch(s, g, sb, P);
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0, [&] {
 			launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.proj + cg, P, (const bf16*)L.out_norm, N, H, Dv, s.m.eps, 1);
 		});
@@ -623,7 +764,7 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 	if (L.ff_kind == SEQ_FF_CLAMPED) {
 		gemm(s, hA, W, 0, L.w_gate_up, W, 0, s.proj, 2L * L.ff, 0, N, 2 * L.ff, W, 1, EPI_F32);
 		run_kernel(s, KD_ELEMENT, (double)N * L.ff * (8 + sizeof(AT)), 0,
-		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * L.ff, 256), 256, 0, a2, s.proj, L.ff, N, L.limit, 0); });
+		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * L.ff, 256), 256, 0, a2, s.proj, L.ff, N, L.limit, 0, 2 * L.ff); });
 		out_product<AT>(s, a2, L.w_down, N, L.ff, oe);
 	} else if (L.ff_kind == SEQ_FF_RELU2) {
 		if (L.in_tail > 0) { // the up rows rode in the mixer's input product
@@ -634,27 +775,41 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		out_product<AT>(s, a2, L.w_down, N, L.ff, oe);
 	} else {
 		// routed experts: logits -> choices and weights -> pairs grouped by expert -> two grouped products around the unit -> weighted sum
-		const int E = L.experts, top = L.top, pairs = N * top, ff = L.ff;
+		const int E = L.experts, Et = E + L.ident, top = L.top, pairs = N * top, ff = L.ff;
 		const float* logits = s.proj;
-		int ldl = E;
+		int ldl = Et;
 		if (L.in_tail > 0) logits = s.proj + in_rows(L), ldl = proj_stride(L); // the router's rows rode in the mixer's input product
 		else {
 			GemmExtra rx;
 			rx.bias = L.b_router;
-			gemm(s, hA, W, 0, L.w_router, W, 0, s.proj, E, 0, N, E, W, 1, EPI_F32, nullptr, -1, true, &rx);
+			gemm(s, hA, W, 0, L.w_router, W, 0, s.proj, Et, 0, N, Et, W, 1, EPI_F32, nullptr, -1, true, &rx);
 		}
-		run_kernel(s, KD_ROUTE, (double)N * E * 4, 0, [&] { launch_k(s, k_seq_moe_route, cdiv(N, 4), 128, 0, logits, ldl, E, top, N, s.moe_sel, s.moe_wt); });
-		run_kernel(s, KD_ROUTE, (double)pairs * 4 * E, 0, [&] { launch_k(s, k_seq_moe_group, E, 256, 0, s.moe_sel, pairs, E, s.moe_seg, s.moe_perm, s.moe_inv); });
+		run_kernel(s, KD_ROUTE, (double)N * Et * 4, 0, [&] {
+			launch_k(s, k_seq_moe_route, cdiv(N, 4), 128, 0, logits, ldl, Et, top, N, s.moe_sel, s.moe_wt, L.route_mode, (const bf16*)L.correction, L.route_scale != 0.f ? L.route_scale : 1.f);
+		});
+		// identity experts get groups of their own behind the real ones: their rows are placed but no product runs over them
+		run_kernel(s, KD_ROUTE, (double)pairs * 4 * Et, 0, [&] { launch_k(s, k_seq_moe_group, Et, 256, 0, s.moe_sel, pairs, Et, s.moe_seg, s.moe_perm, s.moe_inv); });
 		run_kernel(s, KD_ELEMENT, (double)pairs * W * 2 * sizeof(AT), 0,
 		           [&] { launch_k(s, k_seq_moe_gather<AT>, cdiv((long)pairs * W, 256), 256, 0, (AT*)s.moe_x, hA, s.moe_perm, top, pairs, W); });
 		GemmExtra gx;
 		gx.seg = s.moe_seg, gx.x_rows = pairs;
 		gemm(s, s.moe_x, W, 0, L.w_gate_up, W, 2L * ff * W, s.moe_y, 2L * ff, 0, N, 2 * ff, W, E, EPI_F32, nullptr, -1, true, &gx);
 		run_kernel(s, KD_ELEMENT, (double)pairs * ff * (8 + sizeof(AT)), 0,
-		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)pairs * ff, 256), 256, 0, (AT*)s.moe_a, s.moe_y, ff, pairs, 0.f, 1); });
+		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)pairs * ff, 256), 256, 0, (AT*)s.moe_a, s.moe_y, ff, pairs, 0.f, 1, 2 * ff); });
 		gemm(s, s.moe_a, ff, 0, L.w_down, ff, (long)W * ff, s.moe_d, W, 0, N, W, ff, E, EPI_F32, nullptr, -1, true, &gx);
+		if (oe.hc) {
+			// hyper blocks: the shared unit's product is the base of y, the routed sum is formed while the streams are written
+			const int sf = L.shared_ff;
+			if (sf > 0) {
+				gemm(s, hA, W, 0, L.w_sh_gate_up, W, 0, s.proj, 2L * sf, 0, N, 2 * sf, W, 1, EPI_F32);
+				run_kernel(s, KD_ELEMENT, (double)N * sf * (8 + sizeof(AT)), 0, [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * sf, 256), 256, 0, a2, s.proj, sf, N, 0.f, 1, 2 * sf); });
+				gemm(s, a2, sf, 0, L.w_sh_down, sf, 0, s.mo, W, 0, N, W, sf, 1, EPI_F32);
+			}
+			hc_write<AT>(s, *oe.hc, sf > 0 ? s.mo : nullptr, HcMoe{s.moe_d, s.moe_inv, s.moe_sel, s.moe_wt, top, E}, N);
+			return;
+		}
 		run_kernel(s, KD_ELEMENT, (double)N * W * (8 + 4.0 * top) + (oe.res ? (double)N * W * 4 : 0), 0, [&] {
-			launch_k(s, k_seq_moe_combine, cdiv((long)N * W, 256), 256, 0, oe.dst, oe.res, s.moe_d, s.moe_inv, s.moe_wt, top, N, W);
+			launch_k(s, k_seq_moe_combine<AT>, cdiv((long)N * W, 256), 256, 0, oe.dst, oe.res, s.moe_d, s.moe_inv, s.moe_wt, top, N, W, s.moe_sel, E, (const AT*)hA, 0);
 		});
 	}
 }
@@ -663,6 +818,20 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 template <typename AT>
 void layer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest) {
 	const int N = sb.N;
+	if (s.m.block == SEQ_BLOCK_HYPER) {
+		// per sublayer: read the streams (u = sum in[s] x_s, normed), run it into `mo`, write all streams from the old ones and the result
+		hc_read(s, s.hA, nullptr, L.hc1.in, L.norm1, N);
+		mixer_typed<AT>(s, L, r, sb, kv_rows, longest, OutEpi{EPI_F32, nullptr, s.mo, nullptr});
+		hc_write<AT>(s, L.hc1, s.mo, HcMoe{nullptr, nullptr, nullptr, nullptr, 0, 0}, N);
+		if (L.ff > 0) {
+			hc_read(s, s.hA, nullptr, L.hc2.in, L.norm2, N);
+			OutEpi oe{EPI_F32, nullptr, s.mo, nullptr};
+			if (L.ff_kind == SEQ_FF_MOE) oe.hc = &L.hc2;
+			feed_forward<AT>(s, L, sb, oe);
+			if (!oe.hc) hc_write<AT>(s, L.hc2, s.mo, HcMoe{nullptr, nullptr, nullptr, nullptr, 0, 0}, N);
+		}
+		return;
+	}
 	norm(s, s.hA, s.x, nullptr, L.norm1, N);
 	if (s.m.block == SEQ_BLOCK_SERIAL) {
 		mixer_typed<AT>(s, L, r, sb, kv_rows, longest, OutEpi{EPI_DYT_RES, &L.norm1b, s.x, nullptr});
@@ -684,7 +853,7 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 	const int N = sb.N;
 	const bool looped = m.loop_times > 1;
 	run_kernel(s, KD_EMBED, (double)N * m.width * 6, 0,
-	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width, m.embed_scale != 0.f ? m.embed_scale : 1.f); });
+	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width, m.embed_scale != 0.f ? m.embed_scale : 1.f, (const bf16*)m.pos_table, s.d_tpos, s.streams); });
 	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
 		RunState& r = s.runs[ri];
 		const SeqLayer& L = s.layers[r.layer];
@@ -694,11 +863,15 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 		}
 		if (m.exact) layer_typed<float>(s, L, r, sb, kv_rows, longest);
 		else layer_typed<bf16>(s, L, r, sb, kv_rows, longest);
-		if (s.trace)
-			CUDA_CHECK(cudaMemcpyAsync(s.trace_buf + ri * (size_t)N * m.width, s.x, (size_t)N * m.width * sizeof(float), cudaMemcpyDeviceToDevice, s.stream));
+		if (s.trace) { // the residual stream after this run (the sum of the streams when there are several)
+			const size_t n = (size_t)N * m.width;
+			launch_k(s, k_seq_stream_sum, cdiv(n, 256), 256, 0, s.trace_buf + ri * n, s.x, N, m.width, s.streams);
+			CUDA_CHECK(cudaGetLastError());
+		}
 	}
 	if (n_want) {
-		norm(s, s.hW, s.x, s.d_want, m.final_norm, n_want);
+		if (m.block == SEQ_BLOCK_HYPER) hc_read(s, s.hW, s.d_want, nullptr, m.final_norm, n_want);
+		else norm(s, s.hW, s.x, s.d_want, m.final_norm, n_want);
 		gemm(s, s.hW, m.width, 0, m.head, m.width, 0, s.logits, m.vocab, 0, n_want, m.vocab, m.width, 1, EPI_F32);
 	}
 }
@@ -708,15 +881,18 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 void forward_decode_graph(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest) {
 	std::vector<int> key = {sb.N, n_want};
 	size_t part_need = 0;
-	for (const RunState& r : s.runs) {
-		const SeqLayer& L = s.layers[r.layer];
-		if (L.type == SEQ_DELTA || L.type == SEQ_GLA) continue;
+	auto one = [&](const SeqLayer& L) {
+		if (L.type != SEQ_LATENT && L.type != SEQ_WINDOW && L.type != SEQ_GQA) return; // recurrent mixers: nothing to share out
 		const bool lat = L.type == SEQ_LATENT;
 		const int group = lat ? L.heads : L.heads / L.kv_heads, kd = lat ? L.kv_rank : L.dim, vd = lat ? L.kv_rank : L.vdim;
-		const int span = lat || L.window <= 0 ? 0 : L.window + (L.type == SEQ_GQA ? L.keep_first : 0);
-		const int ns = attn_nsplit(s, sb.N, L.heads / attn_tile(group, kd, vd), span, longest);
+		const int ns = attn_nsplit(s, sb.N, L.heads / attn_tile(group, kd, vd), attn_span(L), longest);
 		key.push_back(ns);
 		part_need = std::max(part_need, (size_t)sb.N * L.heads * ns * (vd + 2));
+	};
+	for (const RunState& r : s.runs) {
+		const SeqLayer& L = s.layers[r.layer];
+		if (L.type == SEQ_PAIR) one(L.pair[0]), one(L.pair[1]);
+		else one(L);
 	}
 	ensure_part(s, part_need); // no allocation inside a capture
 	auto it = s.graphs.find(key);
@@ -757,6 +933,13 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 	s.m = *model;
 	s.layers.assign(model->layers, model->layers + model->n_layers);
 	s.m.layers = s.layers.data();
+	s.pairs.reserve(s.layers.size()); // the records a pair points at are copied too
+	for (SeqLayer& L : s.layers)
+		if (L.type == SEQ_PAIR && L.pair) {
+			s.pairs.push_back({L.pair[0], L.pair[1]});
+			L.pair = s.pairs.back().data();
+		}
+	s.streams = s.m.block == SEQ_BLOCK_HYPER && s.m.streams > 1 ? s.m.streams : 1;
 	validate(s);
 	int dev = 0;
 	CUDA_CHECK(cudaGetDevice(&dev));
@@ -795,14 +978,24 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 	s.table.assign((size_t)m.max_seqs * s.max_pages, 0);
 	s.table_dev = (int*)dalloc(s.table.size() * sizeof(int));
 	const size_t rows = (size_t)s.n_pages * m.page;
-	for (RunState& r : s.runs) {
-		const SeqLayer& L = s.layers[r.layer];
+	std::function<void(RunState&, const SeqLayer&)> give = [&](RunState& r, const SeqLayer& L) { // what a run of this mixer owns
+		if (L.type == SEQ_PAIR) {
+			r.sub.assign(2, RunState{r.layer});
+			give(r.sub[0], L.pair[0]), give(r.sub[1], L.pair[1]);
+			return;
+		}
 		if (L.type == SEQ_LATENT) r.cache_a = (float*)dalloc(rows * L.kv_rank * sizeof(float));
 		if (L.type == SEQ_WINDOW || L.type == SEQ_GQA) {
 			r.cache_a = (float*)dalloc(rows * L.kv_heads * L.dim * sizeof(float));
 			r.cache_b = (float*)dalloc(rows * L.kv_heads * L.vdim * sizeof(float));
 		}
-		if (L.type == SEQ_DELTA || L.type == SEQ_WINDOW) {
+		if (L.type == SEQ_GQA && L.dist_bias) { // the penalty per position of distance: 2^(-8 (h+1) / heads)
+			std::vector<float> sl(L.heads);
+			for (int h = 0; h < L.heads; ++h) sl[h] = (float)exp2(-8.0 * (h + 1) / L.heads);
+			r.slopes = (float*)dalloc(L.heads * sizeof(float));
+			CUDA_CHECK(cudaMemcpy(r.slopes, sl.data(), L.heads * sizeof(float), cudaMemcpyHostToDevice));
+		}
+		if (L.type == SEQ_DELTA || L.type == SEQ_WINDOW || L.type == SEQ_MAMBA2) {
 			r.conv_per_slot = (size_t)std::max(L.taps - 1, 0) * conv_channels(L);
 			r.conv = (float*)dalloc(r.conv_per_slot * m.max_seqs * sizeof(float));
 		}
@@ -812,11 +1005,16 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 			const size_t smem = ((size_t)L.dim * L.vdim + 3 * L.dim) * sizeof(float);
 			if (smem > 48 * 1024) CUDA_CHECK(cudaFuncSetAttribute(k_seq_delta_scan, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
 		}
-		if (L.type == SEQ_GLA) { // the scan's own layout: a value column's key channels side by side, padded to its four lanes' share
-			r.delta_per_slot = (size_t)L.heads * L.vdim * gla_ldstate(L.dim);
+		if (L.type == SEQ_GLA || is_lin(L)) { // the scan's own layout: a value column's key channels side by side, padded to its four lanes' share
+			r.delta_per_slot = (size_t)L.heads * (is_lin(L) ? lin_vs(L) : L.vdim) * gla_ldstate(L.dim);
 			r.delta = (float*)dalloc(r.delta_per_slot * m.max_seqs * sizeof(float));
 		}
-	}
+		if (L.type == SEQ_MLSTM) {
+			r.m_per_slot = L.heads;
+			r.mstate = (float*)dalloc(r.m_per_slot * m.max_seqs * sizeof(float));
+		}
+	};
+	for (RunState& r : s.runs) give(r, s.layers[r.layer]);
 	gla_each([&](auto r, auto p) {
 		constexpr int R = decltype(r)::value, P = decltype(p)::value;
 		CUDA_CHECK(cudaFuncSetAttribute(k_seq_gla_scan<R, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gla_smem(R, P)));
@@ -846,13 +1044,23 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 		CUDA_CHECK(cudaMemcpy(s.rot_freq[i], f.data(), half * sizeof(double), cudaMemcpyHostToDevice));
 	}
 	// workspace widths
-	for (const SeqLayer& L : s.layers) {
+	std::function<void(const SeqLayer&)> widths = [&](const SeqLayer& L) {
+		if (L.type == SEQ_PAIR) {
+			widths(L.pair[0]), widths(L.pair[1]);
+			return;
+		}
 		if (L.ff > 0 && L.ff_kind == SEQ_FF_MOE) {
-			s.max_top = std::max(s.max_top, L.top), s.max_experts = std::max(s.max_experts, L.experts), s.w_moe_ff = std::max(s.w_moe_ff, (size_t)L.ff);
-			s.w_proj = std::max(s.w_proj, (size_t)L.experts);
+			s.max_top = std::max(s.max_top, L.top), s.max_experts = std::max(s.max_experts, L.experts + L.ident), s.w_moe_ff = std::max(s.w_moe_ff, (size_t)L.ff);
+			s.w_proj = std::max({s.w_proj, (size_t)L.experts + L.ident, (size_t)2 * L.shared_ff});
+			s.w_a = std::max(s.w_a, (size_t)L.shared_ff);
 		}
 		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim}); // a3 holds the queries
 		if (L.type == SEQ_GLA) s.w_f = std::max({s.w_f, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim}), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.a_rank});
+		if (is_lin(L)) {
+			s.w_f = std::max({s.w_f, (size_t)L.heads * L.dim, (size_t)L.heads * lin_vs(L), (size_t)L.kv_heads * L.dim});
+			s.w_a = std::max(s.w_a, (size_t)L.heads * L.vdim);
+			s.w_lin = std::max(s.w_lin, (size_t)2 * L.heads * L.dim + (size_t)L.heads * lin_vs(L));
+		}
 		s.w_proj = std::max({s.w_proj, (size_t)proj_stride(L), (size_t)2 * L.ff});
 		if (L.ff > 0 && L.ff_kind == SEQ_FF_RELU2 && L.in_tail > 0) s.w_ah = std::max(s.w_ah, (size_t)L.ff);
 		size_t wf = 0, wa = (size_t)L.ff;
@@ -860,6 +1068,14 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 		if (L.type == SEQ_DELTA) wf = std::max((size_t)L.heads * L.dim, (size_t)L.heads * L.vdim), wa = std::max({wa, (size_t)L.heads * L.vdim, (size_t)L.a_rank + L.g_rank});
 		if (L.type == SEQ_WINDOW) wf = (size_t)L.heads * L.dim, wa = std::max({wa, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim});
 		s.w_f = std::max(s.w_f, wf), s.w_a = std::max(s.w_a, wa);
+	};
+	for (const SeqLayer& L : s.layers) {
+		if (L.type == SEQ_PAIR && L.ff > 0) { // the pair's own record carries the layer's feed-forward
+			SeqLayer ffonly = L;
+			ffonly.type = SEQ_GQA, ffonly.heads = ffonly.kv_heads = ffonly.dim = ffonly.vdim = 0, ffonly.no_gate = 1;
+			widths(ffonly);
+		}
+		widths(L);
 	}
 	return sp;
 }
@@ -869,7 +1085,12 @@ extern "C" void calm_b200_seq_release(void* handle) {
 	if (!s) return;
 	cudaStreamSynchronize(s->stream);
 	drop_graphs(*s);
-	for (RunState& r : s->runs) cudaFree(r.cache_a), cudaFree(r.cache_b), cudaFree(r.conv), cudaFree(r.delta);
+	std::function<void(RunState&)> drop = [&](RunState& r) {
+		cudaFree(r.cache_a), cudaFree(r.cache_b), cudaFree(r.conv), cudaFree(r.delta), cudaFree(r.mstate), cudaFree(r.slopes);
+		for (RunState& q : r.sub) drop(q);
+	};
+	for (RunState& r : s->runs) drop(r);
+	cudaFree(s->lin);
 	cudaFree(s->table_dev), cudaFree(s->d_tok), cudaFree(s->d_want), cudaFree(s->d_argmax), cudaFree(s->logits), cudaFree(s->hW);
 	cudaFree(s->part), cudaFree(s->a3), cudaFree(s->att_kb), cudaFree(s->att_vt), cudaFree(s->att_s), cudaFree(s->att_p), cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
 	for (float* p : s->f) cudaFree(p);
@@ -886,10 +1107,13 @@ extern "C" int calm_b200_seq_open(void* handle) {
 	for (int i = 0; i < (int)s.slots.size(); ++i)
 		if (!s.slots[i].open) {
 			s.slots[i].open = true, s.slots[i].len = 0, s.slots[i].pages.clear();
-			for (RunState& r : s.runs) { // a slot that is used again starts from zero state
+			std::function<void(RunState&)> zero = [&](RunState& r) { // a slot that is used again starts from zero state
 				if (r.conv_per_slot) CUDA_CHECK(cudaMemsetAsync(r.conv + r.conv_per_slot * i, 0, r.conv_per_slot * sizeof(float), s.stream));
 				if (r.delta_per_slot) CUDA_CHECK(cudaMemsetAsync(r.delta + r.delta_per_slot * i, 0, r.delta_per_slot * sizeof(float), s.stream));
-			}
+				if (r.m_per_slot) CUDA_CHECK(cudaMemsetAsync(r.mstate + r.m_per_slot * i, 0, r.m_per_slot * sizeof(float), s.stream));
+				for (RunState& q : r.sub) zero(q);
+			};
+			for (RunState& r : s.runs) zero(r);
 			return i;
 		}
 	return -1;
@@ -918,6 +1142,7 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 		if (sl < 0 || sl >= (int)s.slots.size() || !s.slots[sl].open || counts[b] < 1) return -3;
 		for (int c = 0; c < b; ++c)
 			if (slots[c] == sl) return -3;
+		if (m.pos_table && s.slots[sl].len + counts[b] > m.max_positions) return -3; // no position row beyond the table
 		need += cdiv(s.slots[sl].len + counts[b], m.page) - (int)s.slots[sl].pages.size();
 		N += counts[b];
 	}

@@ -17,10 +17,11 @@ def register(architecture: str, loader: Callable) -> None:
 
 
 def _defaults() -> None:
-    from . import bovinex, vimulorn
+    from . import bovinex, vimulorn, zazilix
 
     register(vimulorn.ARCHITECTURE, vimulorn.load)
     register(bovinex.ARCHITECTURE, bovinex.load)
+    register(zazilix.ARCHITECTURE, zazilix.load)
 
 
 def architecture_of(path: str) -> str:

@@ -11,9 +11,9 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SEQ_LATENT, SEQ_DELTA, SEQ_WINDOW, SEQ_GQA, SEQ_GLA = 0, 1, 2, 3, 4
+SEQ_LATENT, SEQ_DELTA, SEQ_WINDOW, SEQ_GQA, SEQ_GLA, SEQ_MLSTM, SEQ_HGRN2, SEQ_MAMBA2, SEQ_PAIR = 0, 1, 2, 3, 4, 5, 6, 7, 8
 NORM_DYT, NORM_RMS = 0, 1
-BLOCK_SERIAL, BLOCK_PARALLEL = 0, 1
+BLOCK_SERIAL, BLOCK_PARALLEL, BLOCK_HYPER = 0, 1, 2
 FF_CLAMPED, FF_RELU2, FF_MOE = 0, 1, 2
 _fptr = C.POINTER(C.c_float)
 _iptr = C.POINTER(C.c_int)
@@ -23,21 +23,34 @@ class SeqNorm(C.Structure):
     _fields_ = [("w", C.c_void_p), ("b", C.c_void_p), ("alpha", C.c_void_p)]
 
 
+class SeqHyper(C.Structure):
+    _fields_ = [("in_", C.c_void_p), ("out", C.c_void_p), ("mix", C.c_void_p)]
+
+
 class SeqLayer(C.Structure):
-    _fields_ = [(n, C.c_int) for n in ("type", "heads", "kv_heads", "dim", "vdim", "q_rank", "kv_rank", "taps", "window", "a_rank", "g_rank", "ff")] + \
+    pass
+
+
+SeqLayer._fields_ = [(n, C.c_int) for n in ("type", "heads", "kv_heads", "dim", "vdim", "q_rank", "kv_rank", "taps", "window", "a_rank", "g_rank", "ff")] + \
                [("scale", C.c_float), ("limit", C.c_float)] + [(n, SeqNorm) for n in ("norm1", "norm1b", "norm2", "norm2b")] + \
                [(n, C.c_void_p) for n in ("w_in", "w_o", "dq_norm", "dkv_norm", "w_uq", "w_ukT", "w_uv", "conv", "w_a2", "w_g2", "a_log", "dt_bias",
                                           "out_norm", "sink", "w_gate_up", "w_down", "b_in", "q_norm", "k_norm", "b_a2")] + \
                [(n, C.c_int) for n in ("keep_first", "rot_dims")] + \
                [(n, C.c_float) for n in ("rot_base", "rot_factor", "rot_original", "rot_fast", "rot_slow", "tau")] + \
-               [(n, C.c_int) for n in ("ff_kind", "experts", "top")] + [(n, C.c_void_p) for n in ("w_router", "b_router")] + [("in_tail", C.c_int)]
+               [(n, C.c_int) for n in ("ff_kind", "experts", "top")] + [(n, C.c_void_p) for n in ("w_router", "b_router")] + [("in_tail", C.c_int)] + \
+               [(n, C.c_int) for n in ("chunk", "dist_bias", "add_one", "v_norm", "no_gate")] + [("gate_cap", C.c_float)] + \
+               [(n, C.c_void_p) for n in ("lower", "conv_b", "skip_d")] + [("norm_groups", C.c_int), ("pair", C.POINTER(SeqLayer)), ("pair_scale", C.c_float * 2),
+                                                                         ("hc1", SeqHyper), ("hc2", SeqHyper), ("route_mode", C.c_int), ("ident", C.c_int),
+                                                                         ("route_scale", C.c_float), ("correction", C.c_void_p), ("shared_ff", C.c_int),
+                                                                         ("w_sh_gate_up", C.c_void_p), ("w_sh_down", C.c_void_p)]
 
 
 class SeqModel(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("vocab", "width", "n_layers", "loop_start", "loop_stop", "loop_times")] + [("eps", C.c_float)] + \
                [(n, C.c_int) for n in ("exact", "max_tokens", "max_seqs", "page")] + \
                [("embed", C.c_void_p), ("head", C.c_void_p), ("final_norm", SeqNorm), ("layers", C.POINTER(SeqLayer)),
-                ("norm_kind", C.c_int), ("norm_offset", C.c_float), ("block", C.c_int), ("embed_scale", C.c_float)]
+                ("norm_kind", C.c_int), ("norm_offset", C.c_float), ("block", C.c_int), ("embed_scale", C.c_float),
+                ("streams", C.c_int), ("norm_scalar", C.c_int), ("pos_table", C.c_void_p), ("max_positions", C.c_int)]
 
 
 _lib = None
@@ -102,15 +115,29 @@ class SeqDeviceModel:
         def norm(prefix: str) -> SeqNorm:  # an RMS norm has only its weight
             return SeqNorm(ptr(prefix), ptr(prefix + ".b") if prefix + ".b" in tensors else None, ptr(prefix + ".alpha") if prefix + ".alpha" in tensors else None)
 
-        self._layers = (SeqLayer * len(layers))()
-        for rec, d in zip(self._layers, layers):
+        self._subs = []  # the records that pairs point at
+
+        def fill(rec: SeqLayer, d: Dict[str, object]) -> None:
             for k, v in d.items():
                 if k in ("norm1", "norm1b", "norm2", "norm2b"):
                     setattr(rec, k, norm(v) if v else SeqNorm())
+                elif k in ("hc1", "hc2"):  # names of the three tensors of a hyper-connection: in, out, mix
+                    setattr(rec, k, SeqHyper(*[ptr(x) for x in v]) if v else SeqHyper())
+                elif k == "pair":
+                    two = (SeqLayer * 2)()
+                    fill(two[0], v[0]), fill(two[1], v[1])
+                    self._subs.append(two)
+                    rec.pair = C.cast(two, C.POINTER(SeqLayer))
+                elif k == "pair_scale":
+                    rec.pair_scale[0], rec.pair_scale[1] = float(v[0]), float(v[1])
                 elif isinstance(v, str) or v is None:
                     setattr(rec, k, ptr(v))
                 else:
                     setattr(rec, k, v)
+
+        self._layers = (SeqLayer * len(layers))()
+        for rec, d in zip(self._layers, layers):
+            fill(rec, d)
         m = SeqModel()
         m.vocab, m.width, m.n_layers = head["vocab"], head["width"], len(layers)
         m.loop_start, m.loop_stop, m.loop_times = head.get("loop_start", 0), head.get("loop_stop", 0), head.get("loop_times", 1)
@@ -118,6 +145,8 @@ class SeqDeviceModel:
         m.embed, m.head, m.final_norm = ptr(head["embed"]), ptr(head["head"]), norm(head["final_norm"])
         m.norm_kind, m.norm_offset = int(head.get("norm_kind", NORM_DYT)), float(head.get("norm_offset", 0.0))
         m.block, m.embed_scale = int(head.get("block", BLOCK_SERIAL)), float(head.get("embed_scale", 1.0))
+        m.streams, m.norm_scalar = int(head.get("streams", 1)), int(head.get("norm_scalar", 0))
+        m.pos_table, m.max_positions = ptr(head.get("pos_table")), int(head.get("max_positions", 0))
         m.layers = C.cast(self._layers, C.POINTER(SeqLayer))
         self.desc = m
         self.vocab, self.width = m.vocab, m.width
@@ -154,7 +183,8 @@ class SeqDeviceModel:
         if rc == -2:
             raise SeqError("the page pool is exhausted: more live tokens than max_tokens")
         if rc != 0:
-            raise SeqError("bad step: a slot that is not open, an empty entry, a token outside the vocabulary or a wanted index outside the batch")
+            raise SeqError("bad step: a slot that is not open, an empty entry, a token outside the vocabulary, a wanted index outside the batch "
+                           "or a sequence longer than the model's position table")
         return out
 
     def argmax(self, n_want: int) -> np.ndarray:

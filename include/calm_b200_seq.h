@@ -22,11 +22,29 @@
  *               sigmoid gate on every output channel.
  *   SEQ_GLA     gated linear attention: a [dim x vdim] fp32 state per head, S <- diag(a) S + k v^T, o = S^T q, with a decay
  *               a = sigmoid(.)^(1/tau) per key channel from a low-rank projection; per-head RMS norm and a SiLU gate on the output.
+ *               Options of SEQ_GQA: `chunk` (a query sees only the keys of its own block of `chunk` positions, counted from position 0),
+ *               `dist_bias` (score -= 2^(-8 (h+1) / heads) * distance), `add_one` (one added to the softmax denominator),
+ *               `v_norm` (every value head divided by its root mean square before it is cached), `no_gate`.
+ *   SEQ_MLSTM   matrix memory with exponential gating: per head a [dim x vdim] fp32 state S, a normaliser n and a running maximum m
+ *               (zero at the start) of the log gates; log input gate cap tanh(./cap), log forget gate logsigmoid(cap tanh(./cap));
+ *               o = S^T q / (max(|n.q|, exp(-m)) + 1e-6); per-head RMS, a weight per output channel, a sigmoid gate.
+ *   SEQ_HGRN2   linear attention whose forget gate f = l + (1 - l) sigmoid(.) per key channel (lower bound l) also writes:
+ *               S <- diag(f) S + (1 - f) v^T, o = S^T silu(q); per-head RMS norm with a weight shared by the heads.
+ *   SEQ_MAMBA2  state-space mixer: one input product [z | x | B | C | dt], a short causal convolution with bias and SiLU over x, B, C,
+ *               dt = softplus(dt + dt_bias), per head S <- exp(-exp(A_log) dt) S + dt B x^T ([state x vdim]), y = S^T C + D x,
+ *               y silu(z), RMS norm in norm_groups equal parts with a weight per channel.  kv_heads = groups of B / C, dim = state.
+ *   SEQ_PAIR    two mixers side by side on the same input (`pair` points at two SeqLayer records, their feed-forward unused):
+ *               pair_scale[0] * first + pair_scale[1] * second.
  * Norms (SeqModel.norm_kind): Dynamic Tanh (tanh(alpha x) w + b), or RMS (x / sqrt(mean x^2 + eps) * (w + norm_offset)).
  * Blocks (SeqModel.block): serial -- norm, mixer, norm, residual add, then the same around the feed-forward; parallel -- one
- * norm whose output both the mixer and the feed-forward read, x <- x + (mixer + feed-forward).
+ * norm whose output both the mixer and the feed-forward read, x <- x + (mixer + feed-forward); hyper -- the residual is `streams`
+ * copies x_1 .. x_S; sublayer q reads u = sum_s in[s] x_s, y = sublayer(norm(u)), and x_t <- sum_s mix[s][t] x_s + out[t] y for all
+ * t at once; the model's output is the sum of the streams.  (One stream with in = out = mix = 1 is the plain pre-norm residual.)
+ * A norm whose weight is a single number for all columns: SeqModel.norm_scalar.  Learned positions: SeqModel.pos_table.
  * Feed-forward (SeqLayer.ff_kind): clamped gated unit, down(relu(up)^2), or a routed mixture of SiLU-gated experts (the `top`
- * highest router scores, mixed by a softmax restricted to those scores).
+ * highest router scores, mixed by a softmax restricted to those scores; or, route_mode 1, a softmax over all router outputs,
+ * the choice made on score + correction, the weights score * route_scale, not renormalised).  The last `ident` router outputs are
+ * identity experts (output = input); a shared unit of the same form (shared_ff) runs for every token and is added.
  * A span of layers can be run several times in a row with the same weights (loop_*), each pass with its own state.
  */
 #ifndef CALM_B200_SEQ_H
@@ -39,9 +57,9 @@
 extern "C" {
 #endif
 
-enum SeqMixer { SEQ_LATENT = 0, SEQ_DELTA = 1, SEQ_WINDOW = 2, SEQ_GQA = 3, SEQ_GLA = 4 };
+enum SeqMixer { SEQ_LATENT = 0, SEQ_DELTA = 1, SEQ_WINDOW = 2, SEQ_GQA = 3, SEQ_GLA = 4, SEQ_MLSTM = 5, SEQ_HGRN2 = 6, SEQ_MAMBA2 = 7, SEQ_PAIR = 8 };
 enum SeqNormKind { SEQ_NORM_DYT = 0, SEQ_NORM_RMS = 1 };
-enum SeqBlock { SEQ_BLOCK_SERIAL = 0, SEQ_BLOCK_PARALLEL = 1 };
+enum SeqBlock { SEQ_BLOCK_SERIAL = 0, SEQ_BLOCK_PARALLEL = 1, SEQ_BLOCK_HYPER = 2 };
 enum SeqFfKind { SEQ_FF_CLAMPED = 0, SEQ_FF_RELU2 = 1, SEQ_FF_MOE = 2 };
 
 /* a norm: bf16 weight[n]; Dynamic Tanh also bf16 bias[n], bf16 alpha[1] (device pointers; NULL for an RMS norm) */
@@ -49,6 +67,13 @@ struct SeqNorm {
 	const void* w;
 	const void* b;
 	const void* alpha;
+};
+
+/* hyper-connection of one sublayer: bf16 in[streams], out[streams], mix[streams][streams] (indexed [from][to]) */
+struct SeqHyper {
+	const void* in;
+	const void* out;
+	const void* mix;
 };
 
 /* One layer.  All matrices are bf16, row-major (out, in), device pointers.  w_in is the layer's input projections
@@ -66,7 +91,8 @@ struct SeqLayer {
 	float limit;         /* clamp of the feed-forward */
 	struct SeqNorm norm1, norm1b, norm2, norm2b;
 	/* SEQ_LATENT: rows [dq | dkv | g];  SEQ_DELTA: [q | k | v | b | a1 | g1];  SEQ_WINDOW: [q | k | v];
-	 * SEQ_GQA: [q | k | v | g];  SEQ_GLA: [q | k | v | g | a1] */
+	 * SEQ_GQA: [q | k | v | g] (no_gate: [q | k | v]);  SEQ_GLA: [q | k | v | g | a1];  SEQ_MLSTM: [q | k | v | g | i | f];
+	 * SEQ_HGRN2: [q | f | v];  SEQ_MAMBA2: [z | x | B | C | dt] */
 	const void* w_in;
 	const void* w_o;       /* (width, heads*vdim) */
 	/* SEQ_LATENT */
@@ -107,6 +133,33 @@ struct SeqLayer {
 	 * product.  in_tail rows appended to w_in (and b_in): SEQ_FF_MOE: the router's `experts` rows (w_router / b_router unused);
 	 * SEQ_FF_RELU2: the `ff` rows of the up projection (w_gate_up unused); 0: the feed-forward runs its own first product */
 	int in_tail;
+	/* SEQ_GQA options */
+	int chunk;             /* > 0: a query at position p sees keys from floor(p / chunk) * chunk on */
+	int dist_bias;         /* 1: score -= 2^(-8 (h+1) / heads) * (query position - key position) */
+	int add_one;           /* 1: one is added to the softmax denominator */
+	int v_norm;            /* 1: each value head is divided by its root mean square (eps, no weight) before it is cached */
+	int no_gate;           /* 1: no output gate (and no gate rows in w_in) */
+	/* SEQ_MLSTM */
+	float gate_cap;        /* soft cap of both gate pre-activations */
+	/* SEQ_HGRN2 */
+	const void* lower;     /* bf16 [heads*dim]: lower bound of the forget gate */
+	/* SEQ_MAMBA2 (also a_log [heads], dt_bias [heads], conv [channels][taps], out_norm [heads*vdim]) */
+	const void* conv_b;    /* bf16 [channels]: bias of the convolution, or NULL */
+	const void* skip_d;    /* bf16 [heads]: y += D x */
+	int norm_groups;       /* the output norm runs over heads*vdim / norm_groups columns at a time */
+	/* SEQ_PAIR */
+	const struct SeqLayer* pair; /* two records */
+	float pair_scale[2];
+	/* SEQ_BLOCK_HYPER */
+	struct SeqHyper hc1, hc2;
+	/* SEQ_FF_MOE extras */
+	int route_mode;        /* 0: softmax over the chosen logits; 1: softmax over all, choice on score + correction, weight = score * route_scale */
+	int ident;             /* identity experts: router outputs experts .. experts + ident - 1 (w_router has experts + ident rows) */
+	float route_scale;
+	const void* correction; /* bf16 [experts + ident] or NULL */
+	int shared_ff;         /* width of the shared unit, 0: none */
+	const void* w_sh_gate_up; /* (2*shared_ff, width) rows [gate | up] */
+	const void* w_sh_down;    /* (width, shared_ff) */
 };
 
 struct SeqModel {
@@ -125,6 +178,10 @@ struct SeqModel {
 	float norm_offset;  /* SEQ_NORM_RMS: added to the stored weight (1 when the checkpoint keeps weights as offsets from one) */
 	int block;          /* enum SeqBlock */
 	float embed_scale;  /* factor on the embedding rows (0 is read as 1) */
+	int streams;        /* SEQ_BLOCK_HYPER: copies of the residual stream (0 is read as 1) */
+	int norm_scalar;    /* 1: every norm weight of the model is one number (bf16 [1]) for all columns */
+	const void* pos_table; /* bf16 (max_positions, width): learned position rows added to the embedding, or NULL */
+	int max_positions;  /* rows of pos_table: no sequence grows beyond */
 };
 
 /* cudaMalloc + copy, like upload_cuda */
