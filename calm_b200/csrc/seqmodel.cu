@@ -75,6 +75,8 @@ struct Seq {
 	void* ah = nullptr;                               // parallel blocks: a dense unit's hidden activations, written by the mixer's input product
 	size_t w_ah = 0;
 	float* mo = nullptr;                              // parallel blocks: the mixer's output until the feed-forward's is added with it; hyper blocks: a sublayer's output
+	float* fsh = nullptr;                             // routed feed-forward with a shared unit: the product [shared gate | shared up | router logits]
+	size_t w_fsh = 0;
 	float* lin = nullptr;                             // scan input of the linear recurrences served by the gated-linear-attention scan: rows [q | k | v]
 	size_t w_lin = 0;
 	int streams = 1;
@@ -282,6 +284,7 @@ void validate(const Seq& s) {
 				if (L.experts < 1 || L.top < 1 || L.top > L.experts + L.ident) CALM_FATAL("seq: layer %d: 1 <= top <= experts", i);
 				if (m.block == SEQ_BLOCK_SERIAL) CALM_FATAL("seq: layer %d: routed experts are not served in serial blocks", i);
 				if (L.ident < 0 || L.top > L.experts + L.ident || L.shared_ff < 0) CALM_FATAL("seq: layer %d: bad identity experts or shared unit", i);
+				if (!L.w_router && L.in_tail == 0 && L.shared_ff == 0) CALM_FATAL("seq: layer %d: the router's rows ride either behind the shared unit's or in w_router", i);
 				if (m.block != SEQ_BLOCK_HYPER && (L.ident || L.shared_ff || L.route_mode)) CALM_FATAL("seq: layer %d: identity experts, the shared unit and route_mode 1 are served in hyper blocks", i);
 			}
 		}
@@ -324,6 +327,7 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 		for (float*& p : s.f) cudaFree(p);
 		if (s.m.block != SEQ_BLOCK_SERIAL) s.mo = (float*)dalloc(cn * s.m.width * sizeof(float));
 		if (s.w_lin) cudaFree(s.lin), s.lin = (float*)dalloc(cn * s.w_lin * sizeof(float));
+		if (s.w_fsh) cudaFree(s.fsh), s.fsh = (float*)dalloc(cn * s.w_fsh * sizeof(float));
 		if (s.w_ah) cudaFree(s.ah), s.ah = dalloc(cn * s.w_ah * act_size(s));
 		if (s.max_top > 0) {
 			cudaFree(s.moe_sel), cudaFree(s.moe_wt), cudaFree(s.moe_y), cudaFree(s.moe_d), cudaFree(s.moe_x), cudaFree(s.moe_a);
@@ -778,8 +782,12 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		const int E = L.experts, Et = E + L.ident, top = L.top, pairs = N * top, ff = L.ff;
 		const float* logits = s.proj;
 		int ldl = Et;
+		const int sf = L.shared_ff, ldsh = 2 * sf + (L.w_router ? 0 : Et);
 		if (L.in_tail > 0) logits = s.proj + in_rows(L), ldl = proj_stride(L); // the router's rows rode in the mixer's input product
-		else {
+		else if (!L.w_router) { // the router's rows ride behind the shared unit's [gate | up]: one product for everything that reads the normed input
+			gemm(s, hA, W, 0, L.w_sh_gate_up, W, 0, s.fsh, ldsh, 0, N, ldsh, W, 1, EPI_F32);
+			logits = s.fsh + 2 * sf, ldl = ldsh;
+		} else {
 			GemmExtra rx;
 			rx.bias = L.b_router;
 			gemm(s, hA, W, 0, L.w_router, W, 0, s.proj, Et, 0, N, Et, W, 1, EPI_F32, nullptr, -1, true, &rx);
@@ -799,10 +807,9 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		gemm(s, s.moe_a, ff, 0, L.w_down, ff, (long)W * ff, s.moe_d, W, 0, N, W, ff, E, EPI_F32, nullptr, -1, true, &gx);
 		if (oe.hc) {
 			// hyper blocks: the shared unit's product is the base of y, the routed sum is formed while the streams are written
-			const int sf = L.shared_ff;
 			if (sf > 0) {
-				gemm(s, hA, W, 0, L.w_sh_gate_up, W, 0, s.proj, 2L * sf, 0, N, 2 * sf, W, 1, EPI_F32);
-				run_kernel(s, KD_ELEMENT, (double)N * sf * (8 + sizeof(AT)), 0, [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * sf, 256), 256, 0, a2, s.proj, sf, N, 0.f, 1, 2 * sf); });
+				if (L.w_router) gemm(s, hA, W, 0, L.w_sh_gate_up, W, 0, s.fsh, ldsh, 0, N, ldsh, W, 1, EPI_F32);
+				run_kernel(s, KD_ELEMENT, (double)N * sf * (8 + sizeof(AT)), 0, [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * sf, 256), 256, 0, a2, s.fsh, sf, N, 0.f, 1, ldsh); });
 				gemm(s, a2, sf, 0, L.w_sh_down, sf, 0, s.mo, W, 0, N, W, sf, 1, EPI_F32);
 			}
 			hc_write<AT>(s, *oe.hc, sf > 0 ? s.mo : nullptr, HcMoe{s.moe_d, s.moe_inv, s.moe_sel, s.moe_wt, top, E}, N);
@@ -1051,7 +1058,8 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 		}
 		if (L.ff > 0 && L.ff_kind == SEQ_FF_MOE) {
 			s.max_top = std::max(s.max_top, L.top), s.max_experts = std::max(s.max_experts, L.experts + L.ident), s.w_moe_ff = std::max(s.w_moe_ff, (size_t)L.ff);
-			s.w_proj = std::max({s.w_proj, (size_t)L.experts + L.ident, (size_t)2 * L.shared_ff});
+			s.w_proj = std::max(s.w_proj, (size_t)L.experts + L.ident);
+			if (L.shared_ff > 0) s.w_fsh = std::max(s.w_fsh, (size_t)2 * L.shared_ff + L.experts + L.ident);
 			s.w_a = std::max(s.w_a, (size_t)L.shared_ff);
 		}
 		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim}); // a3 holds the queries
@@ -1090,7 +1098,7 @@ extern "C" void calm_b200_seq_release(void* handle) {
 		for (RunState& q : r.sub) drop(q);
 	};
 	for (RunState& r : s->runs) drop(r);
-	cudaFree(s->lin);
+	cudaFree(s->lin), cudaFree(s->fsh);
 	cudaFree(s->table_dev), cudaFree(s->d_tok), cudaFree(s->d_want), cudaFree(s->d_argmax), cudaFree(s->logits), cudaFree(s->hW);
 	cudaFree(s->part), cudaFree(s->a3), cudaFree(s->att_kb), cudaFree(s->att_vt), cudaFree(s->att_s), cudaFree(s->att_p), cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
 	for (float* p : s->f) cudaFree(p);

@@ -1,7 +1,8 @@
 """Throughput of the layer-list families at layer sizes of real models (random weights), each beside its closest existing
 model on the same GPU: Vimulorn beside a Llama-shaped stack of the same width, depth, head geometry and feed-forward width in
 fp16 on the calm engine; Bovinex beside Vimulorn at the same width, depth, head geometry, window and feed-forward width on
-the same runtime (both have windowed grouped-query attention and a recurrent mixer with a [dim x vdim] state per head).
+the same runtime (both have windowed grouped-query attention and a recurrent mixer with a [dim x vdim] state per head); Zazilix
+beside Bovinex likewise (both have grouped-query attention with a bounded view, linear recurrences on the same scan kernel and routed experts).
 
 Per size: prompt throughput (one prompt of `prompt` tokens as one step), decode throughput for one sequence and for a
 batch, each after warm-up, timed with CUDA events on the library's stream; then one profiled pass that brackets every
@@ -56,6 +57,21 @@ def bovinex_config(z: dict) -> dict:
             "width": z["width"]}
 
 
+def zazilix_config(z: dict, max_positions: int = 4096) -> dict:
+    """Blocks of [mLSTM, attention in blocks of positions beside HGRN2, Mamba-2], every layer with eight routed experts of half the dense
+    width (two active per token), two identity experts and a shared unit of a quarter of the dense width; four residual streams."""
+    H, D = z["heads"], z["dim"]
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 2}, "router": {"experts": 8, "identity": 2, "top": 2, "scale": 1.5}, "shared": {"ff": z["ff"] // 4}}
+    block = [
+        {"type": "mlstm", "mixer": {"heads": H, "dim": D, "vdim": D, "gate_cap": 15.0}, "mlp": moe},
+        {"type": "parallel", "mixer": {"left": {"heads": H, "kv_heads": z["kv_heads"], "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": z["window"]}},
+                                       "right": {"heads": H, "dim": D, "vdim": D}, "left_scale": 0.7, "right_scale": 0.7}, "mlp": moe},
+        {"type": "mamba2", "mixer": {"heads": H, "vdim": D, "state": 128, "groups": z["kv_heads"], "conv": 4, "norm_groups": z["kv_heads"]}, "mlp": moe},
+    ]
+    return {"architecture": "Zazilix", "embedding": {"scale": math.sqrt(z["width"])}, "layers": block * z["blocks"], "norm": {"eps": 1e-5}, "vocab": z["vocab"],
+            "width": z["width"], "streams": 4, "max_positions": max_positions}
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -76,10 +92,10 @@ def roofline_table(stats: dict, hbm_gbs: float, tflops: float) -> dict:
 
 
 def bench_family(family: str, name: str, prompt: int, batch: int, steps: int, warmup: int, seed: int = 0) -> list:
-    from . import bovinex, vimulorn
+    from . import bovinex, vimulorn, zazilix
 
     z = SIZES[name]
-    mod, cfg = (bovinex, bovinex_config(z)) if family == "bovinex" else (vimulorn, vimulorn_config(z))
+    mod, cfg = {"bovinex": (bovinex, bovinex_config(z)), "zazilix": (zazilix, zazilix_config(z, prompt + steps + 2 * warmup + 64))}.get(family, (vimulorn, vimulorn_config(z)))
     hbm, tf, src = peaks()
     t0 = time.time()
     tensors = mod.random_tensors(cfg, seed)
@@ -174,6 +190,8 @@ def main(sizes, prompt=2048, batch=16, steps=32, warmup=8, twin=True, family="vi
         lines = bench_family(family, name, prompt, batch, steps, warmup)
         if twin and family == "bovinex":
             lines += bench_family("vimulorn", name, prompt, batch, steps, warmup)
+        if twin and family == "zazilix":
+            lines += bench_family("bovinex", name, prompt, batch, steps, warmup)
         if llama:
             lines += bench_llama_twin(name, prompt, steps, warmup)
         for ln in lines:

@@ -118,7 +118,8 @@ def plan(cfg: dict, tensors: Dict[str, torch.Tensor]) -> Tuple[dict, List[dict],
             if sh:
                 sf = int(sh["ff"])
                 rec["shared_ff"] = sf
-                rec["w_sh_gate_up"] = stack(f + "shared.gate_up", [need(f + "shared.gate", [sf, width]), need(f + "shared.up", [sf, width])])
+                # the shared unit's first rows and the router's read the same normed input: one product, the router's rows last
+                rec["w_sh_gate_up"] = stack(f + "shared.in", [need(f + "shared.gate", [sf, width]), need(f + "shared.up", [sf, width]), rec.pop("w_router")])
                 rec["w_sh_down"] = need(f + "shared.down", [width, sf])
         layers.append(rec)
     maxpos = int(cfg["max_positions"])

@@ -158,7 +158,7 @@ struct SeqLayer {
 	float route_scale;
 	const void* correction; /* bf16 [experts + ident] or NULL */
 	int shared_ff;         /* width of the shared unit, 0: none */
-	const void* w_sh_gate_up; /* (2*shared_ff, width) rows [gate | up] */
+	const void* w_sh_gate_up; /* (2*shared_ff, width) rows [gate | up]; with w_router == NULL the router's experts + ident rows follow them (one product) */
 	const void* w_sh_down;    /* (width, shared_ff) */
 };
 

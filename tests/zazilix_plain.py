@@ -33,6 +33,10 @@ def logsigmoid(z):
 
 # ---------------------------------------------------------------- mixers
 
+# What a test may switch off to show that a mechanism reaches the logits (the design itself has all of them on).
+KNOBS = {"sink": True, "penalty": True, "value_norm": True}
+
+
 def mlstm(h, w, p, mx, eps):
     """Matrix memory with exponential input gate and a running maximum that starts at zero."""
     H, D, Dv, cap = mx["heads"], mx["dim"], mx["vdim"], float(mx["gate_cap"])
@@ -68,8 +72,9 @@ def chunk_attention(h, w, p, mx, eps):
     q = rms(h @ w[p + "q"].T, eps) * w[p + "q.norm"]
     k = rms(h @ w[p + "k"].T, eps) * w[p + "k.norm"]
     q, k = q.reshape(T, H, D), k.reshape(T, G, D)
-    v = rms((h @ w[p + "v"].T).reshape(T, G, Dv), eps)
-    sl = slopes(H)
+    v = (h @ w[p + "v"].T).reshape(T, G, Dv)
+    v = rms(v, eps) if KNOBS["value_norm"] else v
+    sl = slopes(H) if KNOBS["penalty"] else np.zeros(H)
     out = np.zeros((T, H, Dv))
     for t in range(T):
         first = (t // size) * size if size > 0 else 0
@@ -77,8 +82,9 @@ def chunk_attention(h, w, p, mx, eps):
         for a in range(H):
             g = a // (H // G)
             s = (k[js, g] @ q[t, a]) * mx["scale"] - sl[a] * (t - js)
-            e = np.exp(s - max(s.max(), 0.0))
-            out[t, a] = (e / (math.exp(-max(s.max(), 0.0)) + e.sum())) @ v[js, g]
+            top = max(s.max(), 0.0)
+            e = np.exp(s - top)
+            out[t, a] = (e / ((math.exp(-top) if KNOBS["sink"] else 0.0) + e.sum())) @ v[js, g]
     return out.reshape(T, H * Dv) @ w[p + "o"].T
 
 
@@ -140,6 +146,9 @@ def gated_unit(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
+MARGINS = []
+
+
 def route(h, w, p, ml):
     """-> (chosen [T, top], weights [T, top]); indices >= experts are identity experts."""
     r = ml["router"]
@@ -148,6 +157,9 @@ def route(h, w, p, ml):
     s /= s.sum(-1, keepdims=True)
     pick = s + w[p + "correction"] if (p + "correction") in w else s
     chosen = np.argsort(-pick, axis=-1, kind="stable")[:, :r["top"]]
+    if r["top"] < pick.shape[-1]:  # how close each token's closest call was: tests in reduced precision leave coin tosses aside
+        ranked = -np.sort(-pick, axis=-1)
+        MARGINS.append(ranked[:, r["top"] - 1] - ranked[:, r["top"]])
     return chosen, np.take_along_axis(s, chosen, -1) * r.get("scale", 1.0)
 
 
