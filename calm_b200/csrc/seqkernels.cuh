@@ -998,11 +998,7 @@ __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 // Router: per token the `top` highest-scoring experts (lowest index wins a tie) and a softmax restricted to their scores.  One warp per token.
 // mode 1: scores are a softmax over ALL `experts` router outputs; the choice is made on score + correction (bf16 [experts] or null), the
 // weights are the chosen scores times `scale`, not renormalised.
-__global__ void k_seq_moe_route(const float* logits, int ld, int experts, int top, int N, int* sel, float* wt, int mode, const bf16* correction, float scale) {
-	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
-	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	const int n = blockIdx.x * (blockDim.x >> 5) + warp;
-	if (n >= N) return;
+__device__ __forceinline__ void moe_route_token(int n, int lane, const float* logits, int ld, int experts, int top, int* sel, float* wt, int mode, const bf16* correction, float scale) {
 	const float* z = logits + (size_t)n * ld;
 	if (mode == 1) {
 		float mx = -INFINITY;
@@ -1051,6 +1047,32 @@ __global__ void k_seq_moe_route(const float* logits, int ld, int experts, int to
 		__syncwarp();
 	}
 	for (int k = lane; k < top; k += 32) wt[(size_t)n * top + k] /= sum;
+}
+__global__ void k_seq_moe_route(const float* logits, int ld, int experts, int top, int N, int* sel, float* wt, int mode, const bf16* correction, float scale) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+	if (n >= N) return;
+	moe_route_token(n, lane, logits, ld, experts, top, sel, wt, mode, correction, scale);
+}
+// Few tokens (a decode step): routing and grouping in ONE CTA.  The warps route the tokens, then thread e places expert e's pairs in
+// token order behind those of the lower experts (same result as k_seq_moe_route followed by k_seq_moe_group).
+#define MOE_SMALL_TOKENS 64
+__global__ void __launch_bounds__(256) k_seq_moe_route_group(const float* logits, int ld, int experts, int top, int N, int* sel, float* wt, int mode, const bf16* correction, float scale,
+                                                             int* seg, int* perm, int* inv) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	for (int n = warp; n < N; n += 8) moe_route_token(n, lane, logits, ld, experts, top, sel, wt, mode, correction, scale);
+	__syncthreads();
+	const int pairs = N * top;
+	for (int e = threadIdx.x; e < experts; e += 256) {
+		int below = 0;
+		for (int i = 0; i < pairs; ++i) below += sel[i] < e;
+		seg[e] = below;
+		if (e == experts - 1) seg[experts] = pairs;
+		for (int i = 0; i < pairs; ++i)
+			if (sel[i] == e) perm[below] = i, inv[i] = below, ++below;
+	}
 }
 // Groups the (token, choice) pairs by expert, pairs of one expert in token order: one CTA per expert counts the pairs of lower
 // experts (its group's first row) and places its own.  seg[e] .. seg[e+1] are expert e's rows, perm[row] = pair, inv[pair] = row.
@@ -1162,7 +1184,7 @@ __global__ void __launch_bounds__(256) k_seq_hc_read(AT* out, const float* x, co
 	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) d[c] = to_act<AT>(mixed(c) * rinv * (ldf(w + (w_len == 1 ? 0 : c)) + offset));
 }
 // Write: x_t <- sum_s mix[s][t] x_s + out[t] y for every stream t at once, from the old streams.  y = base (the sublayer's last product,
-// or null) + the routed experts' weighted sum when `moe` is set (choices in order of rank; identity experts return the input row h).
+// or null) + the routed experts' weighted sum when `moe.y` is set (choices in order of rank; identity experts return the input row h).
 #define HC_MAX 16
 struct HcMoe {
 	const float* y;  // [pairs][width] grouped expert outputs, or null: no routed part
@@ -1171,32 +1193,134 @@ struct HcMoe {
 	const float* wt;
 	int top, real;
 };
-template <typename AT>
-__global__ void k_seq_hc_write(float* x, const float* base, const bf16* mix, const bf16* outw, int N, int width, int streams, HcMoe moe, const AT* h) {
+// One CTA per token.  When `rd.out` is set the same pass also forms the NEXT sublayer's input from the streams it has just written
+// (u = sum_t in[t] x_t, RMS norm, weight), so the streams are not read again: hc_write followed by hc_read in one kernel.  The row of h
+// that identity experts read may be the very row rd.out overwrites: all reads of it come before the barrier, all writes after.
+struct HcRead {
+	void* out;       // [N][width] of the activation type, or null: write only
+	const bf16* in;  // [streams]
+	const bf16* w;
+	int w_len;
+	float offset, eps;
+};
+// (a thread's columns alternate loads and stores of the same matrix, which do not overlap in time, so a thread should have one
+// group of columns, or few)
+#define HC_KEEP 4
+template <int V>
+struct HcVec { float v[V]; };
+template <int V>
+__device__ __forceinline__ HcVec<V> hc_load(const float* p) {
+	HcVec<V> r;
+	if constexpr (V == 4) {
+		const float4 t = *(const float4*)p;
+		r.v[0] = t.x, r.v[1] = t.y, r.v[2] = t.z, r.v[3] = t.w;
+	} else r.v[0] = *p;
+	return r;
+}
+template <int V>
+__device__ __forceinline__ void hc_store(float* p, const HcVec<V>& r) {
+	if constexpr (V == 4) *(float4*)p = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+	else *p = r.v[0];
+}
+// V = 4: width is a multiple of 4 and a thread owns four neighbouring columns (16-byte loads and stores); V = 1: any width
+template <typename AT, int V>
+__global__ void __launch_bounds__(V == 4 ? 512 : 1024) k_seq_hc_write(float* x, const float* base, const bf16* mix, const bf16* outw, int N, int width, int streams, HcMoe moe, const AT* h, HcRead rd) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
-	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-	if (i >= (size_t)N * width) return;
-	const size_t n = i / width, c = i % width;
-	float y = base ? base[i] : 0.f;
-	if (moe.y) {
-		float s = 0.f;
-		for (int k = 0; k < moe.top; ++k) {
-			const float v = moe.sel[n * moe.top + k] >= moe.real ? ldf(h + i) : moe.y[(size_t)moe.inv[n * moe.top + k] * width + c];
-			s = fmaf(moe.wt[n * moe.top + k], v, s);
-		}
-		y += s;
-	}
-	float old[HC_MAX];
-	float* xp = x + n * streams * width + c;
+	__shared__ float red[32];
+	__shared__ float cm[HC_MAX * HC_MAX + 2 * HC_MAX]; // mix, out, in of the next read
+	const int tid = threadIdx.x, nt = blockDim.x;
+	const size_t n = blockIdx.x;
+	for (int i = tid; i < streams * streams; i += nt) cm[i] = ldf(mix + i);
+	for (int i = tid; i < streams; i += nt) cm[HC_MAX * HC_MAX + i] = ldf(outw + i), cm[HC_MAX * HC_MAX + HC_MAX + i] = rd.out ? ldf(rd.in + i) : 0.f;
+	__syncthreads();
+	float* xr = x + n * streams * width;
+	auto column = [&](int c) { // writes the new streams of columns c .. c + V - 1, returns the next read's weighted sum of them
+		const size_t i = n * width + c;
+		HcVec<V> y;
 #pragma unroll
-	for (int s = 0; s < HC_MAX; ++s)
-		if (s < streams) old[s] = xp[(size_t)s * width];
-	for (int t = 0; t < streams; ++t) {
-		float v = 0.f;
+		for (int e = 0; e < V; ++e) y.v[e] = 0.f;
+		if (base) y = hc_load<V>(base + i);
+		if (moe.y) {
+			HcVec<V> sacc;
+#pragma unroll
+			for (int e = 0; e < V; ++e) sacc.v[e] = 0.f;
+			for (int k = 0; k < moe.top; ++k) {
+				HcVec<V> v;
+				if (moe.sel[n * moe.top + k] >= moe.real) {
+#pragma unroll
+					for (int e = 0; e < V; ++e) v.v[e] = ldf(h + i + e);
+				} else v = hc_load<V>(moe.y + (size_t)moe.inv[n * moe.top + k] * width + c);
+				const float wk = moe.wt[n * moe.top + k];
+#pragma unroll
+				for (int e = 0; e < V; ++e) sacc.v[e] = fmaf(wk, v.v[e], sacc.v[e]);
+			}
+#pragma unroll
+			for (int e = 0; e < V; ++e) y.v[e] += sacc.v[e];
+		}
+		HcVec<V> old[HC_MAX];
 #pragma unroll
 		for (int s = 0; s < HC_MAX; ++s)
-			if (s < streams) v = fmaf(ldf(mix + s * streams + t), old[s], v);
-		xp[(size_t)t * width] = fmaf(ldf(outw + t), y, v);
+			if (s < streams) old[s] = hc_load<V>(xr + (size_t)s * width + c);
+		HcVec<V> u;
+#pragma unroll
+		for (int e = 0; e < V; ++e) u.v[e] = 0.f;
+		for (int t = 0; t < streams; ++t) {
+			HcVec<V> v;
+#pragma unroll
+			for (int e = 0; e < V; ++e) v.v[e] = 0.f;
+#pragma unroll
+			for (int s = 0; s < HC_MAX; ++s)
+				if (s < streams) {
+#pragma unroll
+					for (int e = 0; e < V; ++e) v.v[e] = fmaf(cm[s * streams + t], old[s].v[e], v.v[e]);
+				}
+#pragma unroll
+			for (int e = 0; e < V; ++e) v.v[e] = fmaf(cm[HC_MAX * HC_MAX + t], y.v[e], v.v[e]), u.v[e] = fmaf(cm[HC_MAX * HC_MAX + HC_MAX + t], v.v[e], u.v[e]);
+			hc_store<V>(xr + (size_t)t * width + c, v);
+		}
+		return u;
+	};
+	HcVec<V> keep[HC_KEEP];
+	float ss = 0.f;
+#pragma unroll
+	for (int i = 0; i < HC_KEEP; ++i) {
+		const int c = (i * nt + tid) * V;
+		if (c < width) keep[i] = column(c);
+		else {
+#pragma unroll
+			for (int e = 0; e < V; ++e) keep[i].v[e] = 0.f;
+		}
+#pragma unroll
+		for (int e = 0; e < V; ++e) ss = fmaf(keep[i].v[e], keep[i].v[e], ss);
+	}
+	for (int c = (HC_KEEP * nt + tid) * V; c < width; c += nt * V) {
+		const HcVec<V> u = column(c);
+#pragma unroll
+		for (int e = 0; e < V; ++e) ss = fmaf(u.v[e], u.v[e], ss);
+	}
+	if (!rd.out) return;
+	ss = warp_sum(ss);
+	if ((tid & 31) == 0) red[tid >> 5] = ss;
+	__syncthreads();
+	ss = 0.f;
+	for (int i = 0; i < (nt >> 5); ++i) ss += red[i];
+	const float rinv = 1.f / sqrtf(ss / (float)width + rd.eps);
+	AT* d = (AT*)rd.out + n * width;
+#pragma unroll
+	for (int i = 0; i < HC_KEEP; ++i) {
+		const int c = (i * nt + tid) * V;
+		if (c < width) {
+#pragma unroll
+			for (int e = 0; e < V; ++e) d[c + e] = to_act<AT>(keep[i].v[e] * rinv * (ldf(rd.w + (rd.w_len == 1 ? 0 : c + e)) + rd.offset));
+		}
+	}
+	for (int c = (HC_KEEP * nt + tid) * V; c < width; c += nt * V) { // wider rows: the sum is formed again from the streams just written (by this thread)
+#pragma unroll
+		for (int e = 0; e < V; ++e) {
+			float u = 0.f;
+			for (int t = 0; t < streams; ++t) u = fmaf(cm[HC_MAX * HC_MAX + HC_MAX + t], xr[(size_t)t * width + c + e], u);
+			d[c + e] = to_act<AT>(u * rinv * (ldf(rd.w + (rd.w_len == 1 ? 0 : c + e)) + rd.offset));
+		}
 	}
 }
 // out[n] = sum of the streams of token n

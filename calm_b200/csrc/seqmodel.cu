@@ -80,6 +80,7 @@ struct Seq {
 	float* lin = nullptr;                             // scan input of the linear recurrences served by the gated-linear-attention scan: rows [q | k | v]
 	size_t w_lin = 0;
 	int streams = 1;
+	bool h_ready = false;                             // hyper blocks: hA already holds the next sublayer's normed input (the last write formed it)
 	// routed experts: choices and weights per token, groups, and the grouped activations of max_top choices per token
 	int max_top = 0, max_experts = 0;
 	size_t w_moe_ff = 0;
@@ -485,7 +486,9 @@ void attention_products(Seq& s, int kind, const AttArgs& a, bf16* out, const Seq
 	for (int t0 = 0; t0 < count;) {
 		const int q0 = pos0 + t0;
 		int Tb = count - t0;
-		if (a.chunk > 0) Tb = std::min(Tb, (q0 / a.chunk + std::max(1, 256 / a.chunk)) * a.chunk - q0); // a block of queries ends where a block of positions does
+		// a block of queries ends where a block of positions does; about a thousand queries per launch keep the launches few (what a row
+		// does not see of the other blocks is masked, and costs less than more launches would)
+		if (a.chunk > 0) Tb = std::min(Tb, (q0 / a.chunk + std::max(1, 1024 / a.chunk)) * a.chunk - q0);
 		while (Tb > 64 && (size_t)a.group * Tb * (size_t)(q0 + Tb) > budget) Tb = (Tb + 1) / 2;
 		// gathered keys: the kept first positions the block's window has left behind, then everything from the first query's window on
 		int k0 = a.window > 0 ? std::max(0, q0 - a.window + 1) : 0;
@@ -571,12 +574,18 @@ struct OutEpi {
 	const float* res;
 	float scale = 0.f; // != 0: factor on the product
 	const SeqHyper* hc = nullptr; // hyper blocks: the routed feed-forward writes the streams itself (its weighted sum is formed in that kernel)
+	const void* next_in = nullptr;      // ... and in the same kernel reads them for the sublayer that follows: its `in` weights and its norm
+	const SeqNorm* next_norm = nullptr;
 };
+// write the streams from a sublayer's output; with next_in / next_norm also the normed input of the sublayer that follows (into hA)
 template <typename AT>
-void hc_write(Seq& s, const SeqHyper& hc, const float* base, const HcMoe& moe, int N) {
+void hc_write(Seq& s, const SeqHyper& hc, const float* base, const HcMoe& moe, int N, const void* next_in, const SeqNorm* next_norm) {
 	const int W = s.m.width, S = s.streams;
-	run_kernel(s, KD_HYPER, (double)N * W * (8.0 * S + 4 + (moe.y ? 4.0 * moe.top : 0)), 0, [&] {
-		launch_k(s, k_seq_hc_write<AT>, cdiv((long)N * W, 256), 256, 0, s.x, base, (const bf16*)hc.mix, (const bf16*)hc.out, N, W, S, moe, (const AT*)s.hA);
+	HcRead rd{next_norm ? s.hA : nullptr, (const bf16*)next_in, next_norm ? (const bf16*)next_norm->w : nullptr, s.m.norm_scalar ? 1 : W, s.m.norm_offset, s.m.eps};
+	run_kernel(s, KD_HYPER, (double)N * W * (8.0 * S + 4 + (moe.y ? 4.0 * moe.top : 0) + (rd.out ? act_size(s) : 0)), 0, [&] {
+		if (W % 4 == 0) { // four neighbouring columns per thread, one group per thread up to 2048 columns
+			launch_k(s, k_seq_hc_write<AT, 4>, N, std::min(512, cdiv(W / 4, 32) * 32), 0, s.x, base, (const bf16*)hc.mix, (const bf16*)hc.out, N, W, S, moe, (const AT*)s.hA, rd);
+		} else launch_k(s, k_seq_hc_write<AT, 1>, N, std::min(1024, cdiv(W, 32) * 32), 0, s.x, base, (const bf16*)hc.mix, (const bf16*)hc.out, N, W, S, moe, (const AT*)s.hA, rd);
 	});
 }
 template <typename AT>
@@ -792,11 +801,17 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 			rx.bias = L.b_router;
 			gemm(s, hA, W, 0, L.w_router, W, 0, s.proj, Et, 0, N, Et, W, 1, EPI_F32, nullptr, -1, true, &rx);
 		}
-		run_kernel(s, KD_ROUTE, (double)N * Et * 4, 0, [&] {
-			launch_k(s, k_seq_moe_route, cdiv(N, 4), 128, 0, logits, ldl, Et, top, N, s.moe_sel, s.moe_wt, L.route_mode, (const bf16*)L.correction, L.route_scale != 0.f ? L.route_scale : 1.f);
-		});
+		const float rscale = L.route_scale != 0.f ? L.route_scale : 1.f;
 		// identity experts get groups of their own behind the real ones: their rows are placed but no product runs over them
-		run_kernel(s, KD_ROUTE, (double)pairs * 4 * Et, 0, [&] { launch_k(s, k_seq_moe_group, Et, 256, 0, s.moe_sel, pairs, Et, s.moe_seg, s.moe_perm, s.moe_inv); });
+		if (N <= MOE_SMALL_TOKENS) { // a decode step: choices and groups in one launch
+			run_kernel(s, KD_ROUTE, (double)N * Et * 4 + (double)pairs * 4 * Et, 0, [&] {
+				launch_k(s, k_seq_moe_route_group, 1, 256, 0, logits, ldl, Et, top, N, s.moe_sel, s.moe_wt, L.route_mode, (const bf16*)L.correction, rscale, s.moe_seg, s.moe_perm, s.moe_inv);
+			});
+		} else {
+			run_kernel(s, KD_ROUTE, (double)N * Et * 4, 0,
+			           [&] { launch_k(s, k_seq_moe_route, cdiv(N, 4), 128, 0, logits, ldl, Et, top, N, s.moe_sel, s.moe_wt, L.route_mode, (const bf16*)L.correction, rscale); });
+			run_kernel(s, KD_ROUTE, (double)pairs * 4 * Et, 0, [&] { launch_k(s, k_seq_moe_group, Et, 256, 0, s.moe_sel, pairs, Et, s.moe_seg, s.moe_perm, s.moe_inv); });
+		}
 		run_kernel(s, KD_ELEMENT, (double)pairs * W * 2 * sizeof(AT), 0,
 		           [&] { launch_k(s, k_seq_moe_gather<AT>, cdiv((long)pairs * W, 256), 256, 0, (AT*)s.moe_x, hA, s.moe_perm, top, pairs, W); });
 		GemmExtra gx;
@@ -812,7 +827,7 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 				run_kernel(s, KD_ELEMENT, (double)N * sf * (8 + sizeof(AT)), 0, [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * sf, 256), 256, 0, a2, s.fsh, sf, N, 0.f, 1, ldsh); });
 				gemm(s, a2, sf, 0, L.w_sh_down, sf, 0, s.mo, W, 0, N, W, sf, 1, EPI_F32);
 			}
-			hc_write<AT>(s, *oe.hc, sf > 0 ? s.mo : nullptr, HcMoe{s.moe_d, s.moe_inv, s.moe_sel, s.moe_wt, top, E}, N);
+			hc_write<AT>(s, *oe.hc, sf > 0 ? s.mo : nullptr, HcMoe{s.moe_d, s.moe_inv, s.moe_sel, s.moe_wt, top, E}, N, oe.next_in, oe.next_norm);
 			return;
 		}
 		run_kernel(s, KD_ELEMENT, (double)N * W * (8 + 4.0 * top) + (oe.res ? (double)N * W * 4 : 0), 0, [&] {
@@ -823,20 +838,24 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 
 // one run of a layer: norm, mixer, feed-forward, in the model's block form
 template <typename AT>
-void layer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest) {
+void layer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest, const SeqLayer* next) {
 	const int N = sb.N;
 	if (s.m.block == SEQ_BLOCK_HYPER) {
-		// per sublayer: read the streams (u = sum in[s] x_s, normed), run it into `mo`, write all streams from the old ones and the result
-		hc_read(s, s.hA, nullptr, L.hc1.in, L.norm1, N);
+		// per sublayer: read the streams (u = sum in[s] x_s, normed), run it into `mo`, write all streams from the old ones and the result.
+		// Only the first read of a step is a kernel of its own: every write also does the read of the sublayer that follows it.
+		const HcMoe none{nullptr, nullptr, nullptr, nullptr, 0, 0};
+		if (!s.h_ready) hc_read(s, s.hA, nullptr, L.hc1.in, L.norm1, N);
+		const void* after_in = next ? next->hc1.in : nullptr;
+		const SeqNorm* after_norm = next ? &next->norm1 : nullptr;
 		mixer_typed<AT>(s, L, r, sb, kv_rows, longest, OutEpi{EPI_F32, nullptr, s.mo, nullptr});
-		hc_write<AT>(s, L.hc1, s.mo, HcMoe{nullptr, nullptr, nullptr, nullptr, 0, 0}, N);
 		if (L.ff > 0) {
-			hc_read(s, s.hA, nullptr, L.hc2.in, L.norm2, N);
+			hc_write<AT>(s, L.hc1, s.mo, none, N, L.hc2.in, &L.norm2);
 			OutEpi oe{EPI_F32, nullptr, s.mo, nullptr};
-			if (L.ff_kind == SEQ_FF_MOE) oe.hc = &L.hc2;
+			if (L.ff_kind == SEQ_FF_MOE) oe.hc = &L.hc2, oe.next_in = after_in, oe.next_norm = after_norm;
 			feed_forward<AT>(s, L, sb, oe);
-			if (!oe.hc) hc_write<AT>(s, L.hc2, s.mo, HcMoe{nullptr, nullptr, nullptr, nullptr, 0, 0}, N);
-		}
+			if (!oe.hc) hc_write<AT>(s, L.hc2, s.mo, none, N, after_in, after_norm);
+		} else hc_write<AT>(s, L.hc1, s.mo, none, N, after_in, after_norm);
+		s.h_ready = next != nullptr;
 		return;
 	}
 	norm(s, s.hA, s.x, nullptr, L.norm1, N);
@@ -859,6 +878,7 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 	const SeqModel& m = s.m;
 	const int N = sb.N;
 	const bool looped = m.loop_times > 1;
+	s.h_ready = false;
 	run_kernel(s, KD_EMBED, (double)N * m.width * 6, 0,
 	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width, m.embed_scale != 0.f ? m.embed_scale : 1.f, (const bf16*)m.pos_table, s.d_tpos, s.streams); });
 	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
@@ -868,8 +888,9 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 			const size_t n = (size_t)N * m.width;
 			run_kernel(s, KD_ELEMENT, n * 12.0, 0, [&] { launch_k(s, k_seq_add, cdiv(n, 256), 256, 0, s.x, s.x0, n); });
 		}
-		if (m.exact) layer_typed<float>(s, L, r, sb, kv_rows, longest);
-		else layer_typed<bf16>(s, L, r, sb, kv_rows, longest);
+		const SeqLayer* next = ri + 1 < s.runs.size() && !s.runs[ri + 1].readd ? &s.layers[s.runs[ri + 1].layer] : nullptr;
+		if (m.exact) layer_typed<float>(s, L, r, sb, kv_rows, longest, next);
+		else layer_typed<bf16>(s, L, r, sb, kv_rows, longest, next);
 		if (s.trace) { // the residual stream after this run (the sum of the streams when there are several)
 			const size_t n = (size_t)N * m.width;
 			launch_k(s, k_seq_stream_sum, cdiv(n, 256), 256, 0, s.trace_buf + ri * n, s.x, N, m.width, s.streams);
