@@ -171,6 +171,25 @@ __global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limi
 	out[i] = to_act<AT>(g * sigmoidf_(1.702f * g) * (u + 1.f));
 }
 
+// y = silu(gate) up on TWO stacked products in one launch (the routed experts' rows and the shared unit's rows of one feed-forward)
+struct FfPair {
+	const float* gu[2];
+	void* out[2];
+	int ff[2], rows[2], ld[2];
+};
+template <typename AT>
+__global__ void k_seq_ff_act2(FfPair a) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	const size_t n0 = (size_t)a.rows[0] * a.ff[0];
+	const int k = i < n0 ? 0 : 1;
+	if (k) i -= n0;
+	if (i >= (size_t)a.rows[k] * a.ff[k]) return;
+	const size_t n = i / a.ff[k], c = i % a.ff[k];
+	const float g = a.gu[k][n * a.ld[k] + c];
+	((AT*)a.out[k])[i] = to_act<AT>(g * sigmoidf_(g) * a.gu[k][n * a.ld[k] + a.ff[k] + c]);
+}
+
 // ---------------------------------------------------------------- short convolution + activation + per-head norm (+ cache append)
 
 // One of q / k / v: `heads` vectors of `hd` channels starting at column `col` of the projection.
@@ -1222,17 +1241,19 @@ __device__ __forceinline__ void hc_store(float* p, const HcVec<V>& r) {
 	if constexpr (V == 4) *(float4*)p = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
 	else *p = r.v[0];
 }
-// V = 4: width is a multiple of 4 and a thread owns four neighbouring columns (16-byte loads and stores); V = 1: any width
-template <typename AT, int V>
+// V = 4: width is a multiple of 4 and a thread owns four neighbouring columns (16-byte loads and stores); V = 1: any width.
+// SM: the most streams this instance holds in registers (4 or HC_MAX)
+template <typename AT, int V, int SM>
 __global__ void __launch_bounds__(V == 4 ? 512 : 1024) k_seq_hc_write(float* x, const float* base, const bf16* mix, const bf16* outw, int N, int width, int streams, HcMoe moe, const AT* h, HcRead rd) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ float red[32];
-	__shared__ float cm[HC_MAX * HC_MAX + 2 * HC_MAX]; // mix, out, in of the next read
 	const int tid = threadIdx.x, nt = blockDim.x;
 	const size_t n = blockIdx.x;
-	for (int i = tid; i < streams * streams; i += nt) cm[i] = ldf(mix + i);
-	for (int i = tid; i < streams; i += nt) cm[HC_MAX * HC_MAX + i] = ldf(outw + i), cm[HC_MAX * HC_MAX + HC_MAX + i] = rd.out ? ldf(rd.in + i) : 0.f;
-	__syncthreads();
+	// the few coefficients (mix, out, the next read's in) are read where they are used: every lane the same address, served by L1; no
+	// staging and no barrier before the first loads of the streams go out
+	auto c_mix = [&](int s, int t) { return ldf(mix + s * streams + t); };
+	auto c_out = [&](int t) { return ldf(outw + t); };
+	auto c_in = [&](int t) { return rd.out ? ldf(rd.in + t) : 0.f; };
 	float* xr = x + n * streams * width;
 	auto column = [&](int c) { // writes the new streams of columns c .. c + V - 1, returns the next read's weighted sum of them
 		const size_t i = n * width + c;
@@ -1257,9 +1278,9 @@ __global__ void __launch_bounds__(V == 4 ? 512 : 1024) k_seq_hc_write(float* x, 
 #pragma unroll
 			for (int e = 0; e < V; ++e) y.v[e] += sacc.v[e];
 		}
-		HcVec<V> old[HC_MAX];
+		HcVec<V> old[SM];
 #pragma unroll
-		for (int s = 0; s < HC_MAX; ++s)
+		for (int s = 0; s < SM; ++s)
 			if (s < streams) old[s] = hc_load<V>(xr + (size_t)s * width + c);
 		HcVec<V> u;
 #pragma unroll
@@ -1269,13 +1290,15 @@ __global__ void __launch_bounds__(V == 4 ? 512 : 1024) k_seq_hc_write(float* x, 
 #pragma unroll
 			for (int e = 0; e < V; ++e) v.v[e] = 0.f;
 #pragma unroll
-			for (int s = 0; s < HC_MAX; ++s)
+			for (int s = 0; s < SM; ++s)
 				if (s < streams) {
+					const float mx = c_mix(s, t);
 #pragma unroll
-					for (int e = 0; e < V; ++e) v.v[e] = fmaf(cm[s * streams + t], old[s].v[e], v.v[e]);
+					for (int e = 0; e < V; ++e) v.v[e] = fmaf(mx, old[s].v[e], v.v[e]);
 				}
+			const float co = c_out(t), ci = c_in(t);
 #pragma unroll
-			for (int e = 0; e < V; ++e) v.v[e] = fmaf(cm[HC_MAX * HC_MAX + t], y.v[e], v.v[e]), u.v[e] = fmaf(cm[HC_MAX * HC_MAX + HC_MAX + t], v.v[e], u.v[e]);
+			for (int e = 0; e < V; ++e) v.v[e] = fmaf(co, y.v[e], v.v[e]), u.v[e] = fmaf(ci, v.v[e], u.v[e]);
 			hc_store<V>(xr + (size_t)t * width + c, v);
 		}
 		return u;
@@ -1318,7 +1341,7 @@ __global__ void __launch_bounds__(V == 4 ? 512 : 1024) k_seq_hc_write(float* x, 
 #pragma unroll
 		for (int e = 0; e < V; ++e) {
 			float u = 0.f;
-			for (int t = 0; t < streams; ++t) u = fmaf(cm[HC_MAX * HC_MAX + HC_MAX + t], xr[(size_t)t * width + c + e], u);
+			for (int t = 0; t < streams; ++t) u = fmaf(c_in(t), xr[(size_t)t * width + c + e], u);
 			d[c + e] = to_act<AT>(u * rinv * (ldf(rd.w + (rd.w_len == 1 ? 0 : c + e)) + rd.offset));
 		}
 	}

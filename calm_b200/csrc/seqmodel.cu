@@ -583,9 +583,13 @@ void hc_write(Seq& s, const SeqHyper& hc, const float* base, const HcMoe& moe, i
 	const int W = s.m.width, S = s.streams;
 	HcRead rd{next_norm ? s.hA : nullptr, (const bf16*)next_in, next_norm ? (const bf16*)next_norm->w : nullptr, s.m.norm_scalar ? 1 : W, s.m.norm_offset, s.m.eps};
 	run_kernel(s, KD_HYPER, (double)N * W * (8.0 * S + 4 + (moe.y ? 4.0 * moe.top : 0) + (rd.out ? act_size(s) : 0)), 0, [&] {
+		auto go = [&](auto kernel, int threads) { launch_k(s, kernel, N, threads, 0, s.x, base, (const bf16*)hc.mix, (const bf16*)hc.out, N, W, S, moe, (const AT*)s.hA, rd); };
+		const int t4 = std::min(512, cdiv(W / 4, 32) * 32), t1 = std::min(1024, cdiv(W, 32) * 32);
 		if (W % 4 == 0) { // four neighbouring columns per thread, one group per thread up to 2048 columns
-			launch_k(s, k_seq_hc_write<AT, 4>, N, std::min(512, cdiv(W / 4, 32) * 32), 0, s.x, base, (const bf16*)hc.mix, (const bf16*)hc.out, N, W, S, moe, (const AT*)s.hA, rd);
-		} else launch_k(s, k_seq_hc_write<AT, 1>, N, std::min(1024, cdiv(W, 32) * 32), 0, s.x, base, (const bf16*)hc.mix, (const bf16*)hc.out, N, W, S, moe, (const AT*)s.hA, rd);
+			if (S <= 4) go(k_seq_hc_write<AT, 4, 4>, t4);
+			else go(k_seq_hc_write<AT, 4, HC_MAX>, t4);
+		} else if (S <= 4) go(k_seq_hc_write<AT, 1, 4>, t1);
+		else go(k_seq_hc_write<AT, 1, HC_MAX>, t1);
 	});
 }
 template <typename AT>
@@ -817,19 +821,25 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		GemmExtra gx;
 		gx.seg = s.moe_seg, gx.x_rows = pairs;
 		gemm(s, s.moe_x, W, 0, L.w_gate_up, W, 2L * ff * W, s.moe_y, 2L * ff, 0, N, 2 * ff, W, E, EPI_F32, nullptr, -1, true, &gx);
-		run_kernel(s, KD_ELEMENT, (double)pairs * ff * (8 + sizeof(AT)), 0,
-		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)pairs * ff, 256), 256, 0, (AT*)s.moe_a, s.moe_y, ff, pairs, 0.f, 1, 2 * ff); });
-		gemm(s, s.moe_a, ff, 0, L.w_down, ff, (long)W * ff, s.moe_d, W, 0, N, W, ff, E, EPI_F32, nullptr, -1, true, &gx);
 		if (oe.hc) {
-			// hyper blocks: the shared unit's product is the base of y, the routed sum is formed while the streams are written
+			// hyper blocks: the shared unit's product is the base of y, the routed sum is formed while the streams are written; the two units'
+			// activations are one launch
 			if (sf > 0) {
 				if (L.w_router) gemm(s, hA, W, 0, L.w_sh_gate_up, W, 0, s.fsh, ldsh, 0, N, ldsh, W, 1, EPI_F32);
-				run_kernel(s, KD_ELEMENT, (double)N * sf * (8 + sizeof(AT)), 0, [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * sf, 256), 256, 0, a2, s.fsh, sf, N, 0.f, 1, ldsh); });
-				gemm(s, a2, sf, 0, L.w_sh_down, sf, 0, s.mo, W, 0, N, W, sf, 1, EPI_F32);
-			}
+				FfPair fp{{s.moe_y, s.fsh}, {s.moe_a, a2}, {ff, sf}, {pairs, N}, {2 * ff, ldsh}};
+				run_kernel(s, KD_ELEMENT, ((double)pairs * ff + (double)N * sf) * (8 + sizeof(AT)), 0,
+				           [&] { launch_k(s, k_seq_ff_act2<AT>, cdiv((long)pairs * ff + (long)N * sf, 256), 256, 0, fp); });
+			} else
+				run_kernel(s, KD_ELEMENT, (double)pairs * ff * (8 + sizeof(AT)), 0,
+				           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)pairs * ff, 256), 256, 0, (AT*)s.moe_a, s.moe_y, ff, pairs, 0.f, 1, 2 * ff); });
+			gemm(s, s.moe_a, ff, 0, L.w_down, ff, (long)W * ff, s.moe_d, W, 0, N, W, ff, E, EPI_F32, nullptr, -1, true, &gx);
+			if (sf > 0) gemm(s, a2, sf, 0, L.w_sh_down, sf, 0, s.mo, W, 0, N, W, sf, 1, EPI_F32);
 			hc_write<AT>(s, *oe.hc, sf > 0 ? s.mo : nullptr, HcMoe{s.moe_d, s.moe_inv, s.moe_sel, s.moe_wt, top, E}, N, oe.next_in, oe.next_norm);
 			return;
 		}
+		run_kernel(s, KD_ELEMENT, (double)pairs * ff * (8 + sizeof(AT)), 0,
+		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)pairs * ff, 256), 256, 0, (AT*)s.moe_a, s.moe_y, ff, pairs, 0.f, 1, 2 * ff); });
+		gemm(s, s.moe_a, ff, 0, L.w_down, ff, (long)W * ff, s.moe_d, W, 0, N, W, ff, E, EPI_F32, nullptr, -1, true, &gx);
 		run_kernel(s, KD_ELEMENT, (double)N * W * (8 + 4.0 * top) + (oe.res ? (double)N * W * 4 : 0), 0, [&] {
 			launch_k(s, k_seq_moe_combine<AT>, cdiv((long)N * W, 256), 256, 0, oe.dst, oe.res, s.moe_d, s.moe_inv, s.moe_wt, top, N, W, s.moe_sel, E, (const AT*)hA, 0);
 		});
