@@ -16,7 +16,7 @@ from calm_b200 import modelgen as mg  # noqa: E402
 sys.path.insert(0, os.path.join(ROOT, "tools"))
 from make_golden import GOLDEN_SPECS, model_digest  # noqa: E402
 
-HAVE_REF = os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libcalm_ref_cpu.so")) or os.path.isdir("/root/reference")
+HAVE_REF = os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libcalm_ref_cpu.so")) or os.path.exists("/root/reference/src/infer.c")
 
 
 @pytest.mark.parametrize("name", GOLDEN_SPECS)
