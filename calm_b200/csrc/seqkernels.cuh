@@ -1489,11 +1489,16 @@ __global__ void k_seq_lin_out(AT* out, LinOut a, int N) {
 	if (u >= (size_t)N * units) return;
 	const size_t n = u / units;
 	const int c0 = (int)(u % units) * a.unit;
+	// a unit that is one head (mLSTM, HGRN2): the head, its row of o and the mLSTM's denominator are the same for the whole warp
+	const bool one_head = a.unit == a.vdim;
+	const int h0 = c0 / a.vdim;
+	auto denominator = [&](int h) { return fmaxf(fabsf(a.o[n * a.ldo + (size_t)h * a.ohs + a.vdim]), expf(-a.m_t[n * a.heads + h])) + 1e-6f; };
+	const float den0 = a.m_t && one_head ? denominator(h0) : 1.f;
 	auto value = [&](int c) {
-		const int h = c / a.vdim, d = c % a.vdim;
+		const int h = one_head ? h0 : c / a.vdim, d = one_head ? c - c0 : c % a.vdim;
 		const float* oh = a.o + n * a.ldo + (size_t)h * a.ohs;
 		float v = oh[d];
-		if (a.m_t) v /= fmaxf(fabsf(oh[a.vdim]), expf(-a.m_t[n * a.heads + h])) + 1e-6f;
+		if (a.m_t) v /= one_head ? den0 : denominator(h);
 		if (a.skip) v = fmaf(ldf(a.skip_w + h), a.skip[n * inner + c], v);
 		if (a.gate_mode == 3) {
 			const float g = a.gate[n * a.ldg + c];
@@ -1501,6 +1506,8 @@ __global__ void k_seq_lin_out(AT* out, LinOut a, int N) {
 		}
 		return v;
 	};
+	// two passes over the unit, both straight from memory: holding the values in registers between them was measured slower (the
+	// unrolled rounds cost more than the second read, which comes from L1 / L2)
 	float ss = 0.f;
 	for (int i = lane; i < a.unit; i += 32) {
 		const float v = value(c0 + i);

@@ -41,6 +41,9 @@ class Scheduler:
     def add(self, req: Request) -> None:
         if not req.prompt:
             raise ValueError("empty prompt")
+        limit = int(getattr(getattr(self.model, "desc", None), "max_positions", 0) or 0)
+        if limit and len(req.prompt) + req.max_new - 1 > limit:  # the last generated token is never fed back
+            raise ValueError(f"request {req.rid}: {len(req.prompt)} prompt tokens + {req.max_new} new ones pass the model's {limit} positions")
         self.waiting.append(req)
 
     def _pages_for(self, r: Request) -> int:

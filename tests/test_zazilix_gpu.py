@@ -221,7 +221,7 @@ def test_block_edges_sink_penalty_and_value_norm_show(monkeypatch):
 def test_the_first_tokens_of_the_matrix_memory():
     """The running maximum of the log gates starts at zero: with input gates far below zero the first tokens' maximum comes from
     that start, and their outputs are divided by exp(-m) > 1 rather than by their own small normaliser."""
-    cfg = config([mlstm(heads=2, dim=8, vdim=8, cap=12.0, mlp=None)], streams=1)
+    cfg = config([mlstm(heads=2, dim=8, vdim=8, cap=10.0, mlp=None)], streams=1)
     t = weights(cfg, 12)
     t["l0.mix.i.b"] = torch.full_like(t["l0.mix.i.b"], -6.0)
     check_all_ways(cfg, t, tokens(cfg, 24), portions=(3,))
@@ -417,6 +417,10 @@ def test_no_sequence_outgrows_the_position_table():
         with pytest.raises(Exception):
             m.step([s], [[1]], [0])
         assert m.length(s) == 12
+        sched = serving.Scheduler(m)
+        sched.add(serving.Request("fits", tokens(cfg, 4), 9))  # positions 0 .. 11: the ninth new token is not fed back
+        with pytest.raises(ValueError):
+            sched.add(serving.Request("long", tokens(cfg, 4), 10))
 
 
 def test_greedy_generation_through_the_scheduler():
