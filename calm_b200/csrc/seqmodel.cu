@@ -889,7 +889,7 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 	const int N = sb.N;
 	const bool looped = m.loop_times > 1;
 	s.h_ready = false;
-	run_kernel(s, KD_EMBED, (double)N * m.width * 6, 0,
+	run_kernel(s, KD_EMBED, (double)N * m.width * (2.0 + (m.pos_table ? 2.0 : 0.0) + 4.0 * s.streams + (looped ? 4.0 : 0.0)), 0,
 	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width, m.embed_scale != 0.f ? m.embed_scale : 1.f, (const bf16*)m.pos_table, s.d_tpos, s.streams); });
 	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
 		RunState& r = s.runs[ri];
