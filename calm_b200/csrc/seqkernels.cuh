@@ -1391,24 +1391,25 @@ __global__ void k_seq_mlstm_gates(MlstmGates a, SeqBatch sb) {
 			const float fr = a.cap * tanhf(pr[a.fcol + h] / a.cap);
 			lf = -softplusf_(-fr);
 		}
-		float F = lf;
+		// the two scans run in double: a round's sum of log forget gates can reach hundreds, where a float keeps four decimals only
+		double F = lf;
 		for (int o = 1; o < 32; o <<= 1) {
-			const float up = __shfl_up_sync(0xffffffffu, F, o);
+			const double up = __shfl_up_sync(0xffffffffu, F, o);
 			if (lane >= o) F += up;
 		}
-		float A = li - F;
+		double A = live ? (double)li - F : -INFINITY;
 		for (int o = 1; o < 32; o <<= 1) {
-			const float up = __shfl_up_sync(0xffffffffu, A, o);
-			if (lane >= o) A = fmaxf(A, up);
+			const double up = __shfl_up_sync(0xffffffffu, A, o);
+			if (lane >= o) A = fmax(A, up);
 		}
-		const float m = F + fmaxf(m_in, A);
-		float m_prev = __shfl_up_sync(0xffffffffu, m, 1);
+		const double m = F + fmax((double)m_in, A);
+		double m_prev = __shfl_up_sync(0xffffffffu, m, 1);
 		if (lane == 0) m_prev = m_in;
 		if (live) {
 			const size_t o = (size_t)(start + t) * a.heads + h;
-			a.keep[o] = expf(lf + m_prev - m), a.take[o] = expf(li - m), a.m_out[o] = m;
+			a.keep[o] = expf((float)((double)lf + m_prev - m)), a.take[o] = expf((float)((double)li - m)), a.m_out[o] = (float)m;
 		}
-		m_in = __shfl_sync(0xffffffffu, m, min(31, cnt - t0 - 1));
+		m_in = (float)__shfl_sync(0xffffffffu, m, min(31, cnt - t0 - 1));
 	}
 	if (lane == 0) *mp = m_in;
 }
