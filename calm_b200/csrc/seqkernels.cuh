@@ -50,15 +50,28 @@ __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log
 // ---------------------------------------------------------------- embedding, norms, small element-wise kernels
 
 // x[n] = E[tok[n]] * scale (+ P[position of n], a learned position row, not scaled), written to every one of `streams` copies
-// (and a second copy when a looped span re-adds the embedding)
-__global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* tok, int N, int width, float scale, const bf16* pos_table, const int* tpos, int streams) {
+// (and a second copy when a looped span re-adds the embedding).  With a bigram table, row (previous token * mul_prev + token * mul_cur)
+// mod buckets of it is added as well; a sequence's first token (tprev < 0) takes row `buckets`, the table's last.
+struct EmbedBigram {
+	const bf16* table; // (buckets + 1, width) or null
+	const int* tprev;  // [N] the token before each packed token in its sequence, -1 for a first token
+	int buckets, mul_prev, mul_cur;
+};
+__global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* tok, int N, int width, float scale, const bf16* pos_table, const int* tpos, int streams, EmbedBigram bg) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int n = blockIdx.x;
 	const bf16* e = table + (size_t)tok[n] * width;
 	const bf16* pr = pos_table ? pos_table + (size_t)tpos[n] * width : nullptr;
+	const bf16* br = nullptr;
+	if (bg.table) {
+		const int prev = bg.tprev[n];
+		const long long row = prev < 0 ? bg.buckets : ((long long)prev * bg.mul_prev + (long long)tok[n] * bg.mul_cur) % bg.buckets;
+		br = bg.table + (size_t)row * width;
+	}
 	for (int i = threadIdx.x; i < width; i += blockDim.x) {
 		float v = ldf(e + i) * scale;
 		if (pr) v += ldf(pr + i);
+		if (br) v += ldf(br + i);
 		for (int s = 0; s < streams; ++s) x[((size_t)n * streams + s) * width + i] = v;
 		if (x0) x0[(size_t)n * width + i] = v;
 	}
@@ -153,7 +166,7 @@ __global__ void k_seq_cast_cols(AT* out, const float* src, int lds, int col, int
 }
 
 // feed-forward unit on the stacked [gate | up] product.  mode 0: g = min(gate, L), u = clamp(up, -L, L), y = g sigmoid(1.702 g) (u + 1);
-// mode 1: y = silu(gate) up
+// mode 1: y = silu(gate) up; mode 2: y = gelu(gate) up, gelu(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 // (ld: row stride of gu, 2 * ff when the product holds nothing else)
 template <typename AT>
 __global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limit, int mode, int ld) {
@@ -164,6 +177,11 @@ __global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limi
 	if (mode == 1) {
 		const float g = gu[n * ld + c];
 		out[i] = to_act<AT>(g * sigmoidf_(g) * gu[n * ld + ff + c]);
+		return;
+	}
+	if (mode == 2) {
+		const float g = gu[n * ld + c];
+		out[i] = to_act<AT>(0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * gu[n * ld + ff + c]);
 		return;
 	}
 	const float g = fminf(gu[n * ld + c], limit);
@@ -953,10 +971,11 @@ struct QkArgs {
 	float* kc;          // cache rows [kv_heads*dim]
 	float* vc;          // cache rows [kv_heads*vdim]
 	int v_norm = 0;     // 1: every value head is divided by its root mean square over vdim (eps inside the root, no weight)
+	int per_head = 0;   // 1: the RMS norms run over each head's `dim` channels, qw / kw are [dim] and serve every head
 };
 __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
-	extern __shared__ float cs[]; // [rot_dims/2] cos, [rot_dims/2] sin
+	extern __shared__ float cs[]; // [rot_dims/2] cos, [rot_dims/2] sin, then (per_head) [heads + kv_heads] reciprocal root mean squares
 	__shared__ float red[2][8];
 	const int n = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int Q = a.heads * a.dim, K = a.kv_heads * a.dim, Vn = a.kv_heads * a.vdim, half = a.rot_dims / 2;
@@ -969,7 +988,16 @@ __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 		cs[i] = (float)c * a.mag, cs[half + i] = (float)s * a.mag;
 	}
 	float sq = 0.f, sk = 0.f;
-	if (a.qw) {
+	float* rh = cs + 2 * max(half, 1);
+	if (a.qw && a.per_head) { // one warp per head vector, query heads first: the key heads follow them in the projection
+		for (int u = warp; u < a.heads + a.kv_heads; u += (int)(blockDim.x >> 5)) {
+			const float* src = pr + (size_t)u * a.dim;
+			float ss = 0.f;
+			for (int i = lane; i < a.dim; i += 32) ss = fmaf(src[i], src[i], ss);
+			ss = warp_sum(ss);
+			if (lane == 0) rh[u] = 1.f / sqrtf(ss / (float)a.dim + a.eps);
+		}
+	} else if (a.qw) {
 		for (int i = tid; i < Q; i += blockDim.x) sq = fmaf(pr[i], pr[i], sq);
 		for (int i = tid; i < K; i += blockDim.x) sk = fmaf(pr[Q + i], pr[Q + i], sk);
 		sq = warp_sum(sq), sk = warp_sum(sk);
@@ -977,7 +1005,7 @@ __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 	}
 	__syncthreads();
 	float rq = 1.f, rk = 1.f;
-	if (a.qw) {
+	if (a.qw && !a.per_head) {
 		sq = sk = 0.f;
 		for (int w = 0; w < (int)(blockDim.x >> 5); ++w) sq += red[0][w], sk += red[1][w];
 		rq = 1.f / sqrtf(sq / (float)Q + a.eps), rk = 1.f / sqrtf(sk / (float)K + a.eps);
@@ -987,12 +1015,13 @@ __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 		const bool isq = e < Q;
 		const int c = isq ? e : e - Q, d = c % a.dim;
 		const bf16* w = isq ? a.qw : a.kw;
-		const float r = isq ? rq : rk;
+		const float r = a.per_head && w ? rh[e / a.dim] : isq ? rq : rk; // e / dim: query heads, then key heads
 		const float* src = pr + (isq ? 0 : Q);
-		float v = src[c] * r * (w ? ldf(w + c) : 1.f);
+		const int wo = a.per_head ? c - d : 0; // a weight shared by the heads is indexed by the channel inside the head
+		float v = src[c] * r * (w ? ldf(w + c - wo) : 1.f);
 		if (d < a.rot_dims) {
 			const int i = d < half ? d : d - half, o = d < half ? c + half : c - half;
-			const float other = src[o] * r * (w ? ldf(w + o) : 1.f);
+			const float other = src[o] * r * (w ? ldf(w + o - wo) : 1.f);
 			v = d < half ? v * cs[i] - other * cs[half + i] : v * cs[i] + other * cs[half + i];
 		}
 		if (isq) a.q[(size_t)n * Q + c] = v;
@@ -1016,7 +1045,7 @@ __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 // ---------------------------------------------------------------- routed experts
 // Router: per token the `top` highest-scoring experts (lowest index wins a tie) and a softmax restricted to their scores.  One warp per token.
 // mode 1: scores are a softmax over ALL `experts` router outputs; the choice is made on score + correction (bf16 [experts] or null), the
-// weights are the chosen scores times `scale`, not renormalised.
+// weights are the chosen scores times `scale`, not renormalised.  mode 2: scores are sigmoid(output), choice and weight alike.
 __device__ __forceinline__ void moe_route_token(int n, int lane, const float* logits, int ld, int experts, int top, int* sel, float* wt, int mode, const bf16* correction, float scale) {
 	const float* z = logits + (size_t)n * ld;
 	if (mode == 1) {
@@ -1041,6 +1070,26 @@ __device__ __forceinline__ void moe_route_token(int n, int lane, const float* lo
 				if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi, bs = os;
 			}
 			if (lane == 0) sel[(size_t)n * top + k] = bi, wt[(size_t)n * top + k] = bs * scale;
+			__syncwarp();
+		}
+		return;
+	}
+	if (mode == 2) { // scores sigmoid(z); the `top` largest, each weighted by its own score
+		for (int k = 0; k < top; ++k) {
+			float bv = -INFINITY;
+			int bi = 0x7fffffff;
+			for (int e = lane; e < experts; e += 32) {
+				bool taken = false;
+				for (int j = 0; j < k; ++j) taken |= sel[(size_t)n * top + j] == e;
+				const float sc = sigmoidf_(z[e]);
+				if (!taken && sc > bv) bv = sc, bi = e;
+			}
+			for (int o = 16; o > 0; o >>= 1) {
+				const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+				const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+				if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+			}
+			if (lane == 0) sel[(size_t)n * top + k] = bi, wt[(size_t)n * top + k] = bv * scale;
 			__syncwarp();
 		}
 		return;
@@ -1346,6 +1395,56 @@ __global__ void __launch_bounds__(V == 4 ? 512 : 1024) k_seq_hc_write(float* x, 
 		}
 	}
 }
+// Post-norm blocks: x[n] += y / sqrt(mean(y^2) + eps) * (w + offset), where y = base (a sublayer's last product, or null) + the routed
+// experts' sum when `moe.y` is set (choices in order of rank, each times its weight, or times one when moe.wt is null: the weight went
+// in at the expert's input).  The same pass writes the new row of x in the activation type: the input of the sublayer that follows.
+// One CTA per token; a thread keeps its columns of y in registers (rows wider than blockDim * RMS_KEEP form y a second time).
+template <typename AT>
+__global__ void __launch_bounds__(256) k_seq_post_norm(float* x, AT* act, const float* base, HcMoe moe, const bf16* w, float offset, float eps, int N, int width) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	__shared__ float red[8];
+	const int tid = threadIdx.x, nt = blockDim.x;
+	const size_t n = blockIdx.x;
+	auto yval = [&](int c) {
+		float y = base ? base[n * width + c] : 0.f;
+		if (moe.y)
+			for (int k = 0; k < moe.top; ++k) {
+				const float v = moe.y[(size_t)moe.inv[n * moe.top + k] * width + c];
+				y = moe.wt ? fmaf(moe.wt[n * moe.top + k], v, y) : y + v;
+			}
+		return y;
+	};
+	float keep[RMS_KEEP];
+	float ss = 0.f;
+#pragma unroll
+	for (int i = 0; i < RMS_KEEP; ++i) {
+		const int c = i * nt + tid;
+		keep[i] = c < width ? yval(c) : 0.f;
+		ss = fmaf(keep[i], keep[i], ss);
+	}
+	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) {
+		const float y = yval(c);
+		ss = fmaf(y, y, ss);
+	}
+	ss = warp_sum(ss);
+	if ((tid & 31) == 0) red[tid >> 5] = ss;
+	__syncthreads();
+	ss = 0.f;
+	for (int i = 0; i < (nt >> 5); ++i) ss += red[i]; // every thread adds the warps' sums in the same order
+	const float rinv = 1.f / sqrtf(ss / (float)width + eps);
+	float* xr = x + n * width;
+	AT* ar = act + n * width;
+	auto put = [&](int c, float y) {
+		const float v = xr[c] + y * rinv * (ldf(w + c) + offset);
+		xr[c] = v, ar[c] = to_act<AT>(v);
+	};
+#pragma unroll
+	for (int i = 0; i < RMS_KEEP; ++i) {
+		const int c = i * nt + tid;
+		if (c < width) put(c, keep[i]);
+	}
+	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) put(c, yval(c));
+}
 // out[n] = sum of the streams of token n
 __global__ void k_seq_stream_sum(float* out, const float* x, int N, int width, int streams) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
@@ -1552,6 +1651,10 @@ struct GemmArgs {
 	void* Y2;
 	long ldy2;
 	float out_scale = 0.f;   // != 0: the accumulator (after the bias) is multiplied by it
+	const float* rs = nullptr; // a factor per row on the accumulator (after the bias): rs[(rs_idx ? rs_idx[row] : row) * rs_ld], through a sigmoid when rs_act is 1
+	const int* rs_idx = nullptr;
+	long rs_ld = 1;
+	int rs_act = 0;
 };
 // rows of batch z: first row and count
 struct GemmRows {
@@ -1568,6 +1671,10 @@ __device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, const GemmR
 	const size_t o = (size_t)z * a.ybs + (size_t)(gr.base + n) * a.ldy + m;
 	if (a.bias) acc += ldf(a.bias + (size_t)z * a.M + m);
 	if (a.out_scale != 0.f) acc *= a.out_scale;
+	if (a.rs) {
+		const float f = a.rs[(size_t)(a.rs_idx ? a.rs_idx[gr.base + n] : gr.base + n) * a.rs_ld];
+		acc *= a.rs_act ? sigmoidf_(f) : f;
+	}
 	if (a.split > 0 && m >= a.split) {
 		const float r = fmaxf(acc, 0.f);
 		((AT*)a.Y2)[(size_t)(gr.base + n) * a.ldy2 + (m - a.split)] = to_act<AT>(r * r);

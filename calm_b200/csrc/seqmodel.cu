@@ -43,6 +43,7 @@ struct RunState {
 struct Slot {
 	bool open = false;
 	int len = 0;
+	int last_tok = -1; // the token before the next one (the bigram embedding reads it); -1: the sequence is empty
 	std::vector<int> pages;
 };
 
@@ -51,8 +52,7 @@ struct Seq {
 	std::vector<SeqLayer> layers;
 	std::vector<std::array<SeqLayer, 2>> pairs;
 	std::vector<RunState> runs;
-	std::vector<double*> rot_freq; // per layer: angle step of every rotated pair (SEQ_GQA), device
-	std::vector<float> rot_mag;    // per layer: factor on cos and sin
+	std::map<const SeqLayer*, std::pair<double*, float>> rot; // per SEQ_GQA record (a layer's, or one of a pair's): angle step of every rotated pair (device), factor on cos and sin
 	cudaStream_t stream = nullptr;
 	int sms = 0;
 	bool tc = false; // tcgen05 products available (bf16 mode)
@@ -66,7 +66,7 @@ struct Seq {
 
 	// per-step batch description
 	int cap_tokens = 0, cap_seqs = 0, cap_want = 0;
-	int *d_tok = nullptr, *d_tslot = nullptr, *d_tpos = nullptr, *d_tfirst = nullptr, *d_sstart = nullptr, *d_scount = nullptr, *d_spos0 = nullptr, *d_sslot = nullptr,
+	int *d_tok = nullptr, *d_tslot = nullptr, *d_tpos = nullptr, *d_tfirst = nullptr, *d_tprev = nullptr, *d_sstart = nullptr, *d_scount = nullptr, *d_spos0 = nullptr, *d_sslot = nullptr,
 	    *d_want = nullptr, *d_argmax = nullptr;
 	std::vector<int> h_meta;
 
@@ -160,7 +160,7 @@ size_t in_rows(const SeqLayer& L) {
 	switch (L.type) {
 	case SEQ_LATENT: return (size_t)L.q_rank + L.kv_rank + L.heads;
 	case SEQ_DELTA: return (size_t)2 * L.kv_heads * L.dim + (size_t)L.heads * L.vdim + L.heads + L.a_rank + L.g_rank;
-	case SEQ_GQA: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim + (L.no_gate ? 0 : (size_t)L.heads * L.vdim);
+	case SEQ_GQA: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim + (L.no_gate ? 0 : L.gate_per_head ? (size_t)L.heads : (size_t)L.heads * L.vdim);
 	case SEQ_MLSTM: return (size_t)2 * L.heads * L.dim + (size_t)2 * L.heads * L.vdim + 2 * L.heads;
 	case SEQ_HGRN2: return (size_t)2 * L.heads * L.dim + (size_t)L.heads * L.vdim;
 	case SEQ_MAMBA2: return (size_t)2 * L.heads * L.vdim + (size_t)2 * L.kv_heads * L.dim + L.heads;
@@ -257,7 +257,8 @@ void validate_mixer(const Seq& s, int i, const SeqLayer& L, bool inner) {
 			if (L.a_rank < 1) CALM_FATAL("seq: layer %d: the decay rank must be positive", i);
 			if (!(L.tau > 0.f)) CALM_FATAL("seq: layer %d: tau must be positive", i);
 		} else CALM_FATAL("seq: layer %d: unknown mixer %d", i, L.type);
-		if ((L.type != SEQ_GQA && (L.chunk || L.dist_bias || L.add_one || L.v_norm || L.no_gate)) || L.chunk < 0) CALM_FATAL("seq: layer %d: chunk, dist_bias, add_one, v_norm and no_gate are options of SEQ_GQA", i);
+		if ((L.type != SEQ_GQA && (L.chunk || L.dist_bias || L.add_one || L.v_norm || L.no_gate || L.qk_per_head || L.gate_per_head || L.scores_f32)) || L.chunk < 0)
+			CALM_FATAL("seq: layer %d: chunk, dist_bias, add_one, v_norm, no_gate, qk_per_head, gate_per_head and scores_f32 are options of SEQ_GQA", i);
 		(void)m;
 	}
 }
@@ -276,9 +277,10 @@ void validate(const Seq& s) {
 		validate_mixer(s, i, L, false);
 		if (m.block == SEQ_BLOCK_HYPER && (!L.hc1.in || !L.hc1.out || !L.hc1.mix || (L.ff > 0 && (!L.hc2.in || !L.hc2.out || !L.hc2.mix))))
 			CALM_FATAL("seq: layer %d: hyper blocks need in, out and mix of every sublayer", i);
-		if (m.block != SEQ_BLOCK_HYPER && (L.type == SEQ_PAIR || is_lin(L))) CALM_FATAL("seq: layer %d: this mixer is served in hyper blocks", i);
+		if (m.block != SEQ_BLOCK_HYPER && m.block != SEQ_BLOCK_POST && (L.type == SEQ_PAIR || is_lin(L))) CALM_FATAL("seq: layer %d: this mixer is served in hyper and post-norm blocks", i);
 		if (L.ff > 0) {
-			if (L.ff_kind < SEQ_FF_CLAMPED || L.ff_kind > SEQ_FF_MOE) CALM_FATAL("seq: layer %d: unknown feed-forward kind %d", i, L.ff_kind);
+			if (L.ff_kind < SEQ_FF_CLAMPED || L.ff_kind > SEQ_FF_GATED) CALM_FATAL("seq: layer %d: unknown feed-forward kind %d", i, L.ff_kind);
+			if (L.ff_kind == SEQ_FF_GATED && L.ff_act != SEQ_ACT_SILU && L.ff_act != SEQ_ACT_GELU_TANH) CALM_FATAL("seq: layer %d: unknown activation %d", i, L.ff_act);
 			if (L.in_tail != 0 && (m.block != SEQ_BLOCK_PARALLEL || L.in_tail != (L.ff_kind == SEQ_FF_MOE ? L.experts : L.ff_kind == SEQ_FF_RELU2 ? L.ff : -1)))
 				CALM_FATAL("seq: layer %d: in_tail must be the router's or the up projection's row count, in a parallel block", i);
 			if (L.ff_kind == SEQ_FF_MOE) {
@@ -286,12 +288,20 @@ void validate(const Seq& s) {
 				if (m.block == SEQ_BLOCK_SERIAL) CALM_FATAL("seq: layer %d: routed experts are not served in serial blocks", i);
 				if (L.ident < 0 || L.top > L.experts + L.ident || L.shared_ff < 0) CALM_FATAL("seq: layer %d: bad identity experts or shared unit", i);
 				if (!L.w_router && L.in_tail == 0 && L.shared_ff == 0) CALM_FATAL("seq: layer %d: the router's rows ride either behind the shared unit's or in w_router", i);
-				if (m.block != SEQ_BLOCK_HYPER && (L.ident || L.shared_ff || L.route_mode)) CALM_FATAL("seq: layer %d: identity experts, the shared unit and route_mode 1 are served in hyper blocks", i);
+				if (m.block != SEQ_BLOCK_HYPER && (L.ident || L.route_mode == 1)) CALM_FATAL("seq: layer %d: identity experts and route_mode 1 are served in hyper blocks", i);
+				if (m.block != SEQ_BLOCK_HYPER && m.block != SEQ_BLOCK_POST && L.shared_ff) CALM_FATAL("seq: layer %d: the shared unit is served in hyper and post-norm blocks", i);
+				if (L.route_mode < 0 || L.route_mode > 2) CALM_FATAL("seq: layer %d: unknown route_mode %d", i, L.route_mode);
+				if (m.block != SEQ_BLOCK_POST && (L.expert_act || L.weight_input || L.shared_gate)) CALM_FATAL("seq: layer %d: relu^2 experts, weights on the input and the gated shared unit are served in post-norm blocks", i);
+				if (m.block == SEQ_BLOCK_POST && L.shared_ff && !L.expert_act) CALM_FATAL("seq: layer %d: post-norm blocks serve the shared unit in the relu^2 form", i);
+				if (L.weight_input && !L.expert_act) CALM_FATAL("seq: layer %d: a weight on the input is served for relu^2 experts", i);
+				if (L.shared_gate && !L.shared_ff) CALM_FATAL("seq: layer %d: a shared gate needs a shared unit", i);
 			}
 		}
 	}
 	if (m.norm_kind != SEQ_NORM_DYT && m.norm_kind != SEQ_NORM_RMS) CALM_FATAL("seq: unknown norm kind %d", m.norm_kind);
-	if (m.block != SEQ_BLOCK_SERIAL && m.block != SEQ_BLOCK_PARALLEL && m.block != SEQ_BLOCK_HYPER) CALM_FATAL("seq: unknown block form %d", m.block);
+	if (m.block < SEQ_BLOCK_SERIAL || m.block > SEQ_BLOCK_POST) CALM_FATAL("seq: unknown block form %d", m.block);
+	if (m.block == SEQ_BLOCK_POST && (m.norm_kind != SEQ_NORM_RMS || m.norm_scalar || m.loop_times > 1)) CALM_FATAL("seq: post-norm blocks use the RMS norm with a weight per column, outside looped spans");
+	if (m.bigram && (m.bigram_buckets < 1 || m.bigram_mul_prev < 0 || m.bigram_mul_cur < 0)) CALM_FATAL("seq: a bigram table needs buckets >= 1 and multipliers >= 0");
 	if (m.block == SEQ_BLOCK_HYPER && m.norm_kind != SEQ_NORM_RMS) CALM_FATAL("seq: hyper blocks use the RMS norm");
 	if (m.block == SEQ_BLOCK_SERIAL && m.norm_kind != SEQ_NORM_DYT)
 		CALM_FATAL("seq: serial blocks fold their second norm into the product before it, which only a norm without row statistics (Dynamic Tanh) allows");
@@ -308,9 +318,9 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 		const int cn = std::max(N, s.cap_tokens), cb = std::max(B, s.cap_seqs);
 		CUDA_CHECK(cudaStreamSynchronize(s.stream));
 		cudaFree(s.d_tok);
-		s.d_tok = (int*)dalloc(((size_t)5 * cn + 4 * cb) * sizeof(int));
-		s.d_tslot = s.d_tok + cn, s.d_tpos = s.d_tslot + cn, s.d_tfirst = s.d_tpos + cn, s.d_skip = s.d_tfirst + cn;
-		s.d_sstart = s.d_skip + cn, s.d_scount = s.d_sstart + cb, s.d_spos0 = s.d_scount + cb, s.d_sslot = s.d_spos0 + cb;
+		s.d_tok = (int*)dalloc(((size_t)6 * cn + 4 * cb) * sizeof(int));
+		s.d_tslot = s.d_tok + cn, s.d_tpos = s.d_tslot + cn, s.d_tfirst = s.d_tpos + cn, s.d_skip = s.d_tfirst + cn, s.d_tprev = s.d_skip + cn;
+		s.d_sstart = s.d_tprev + cn, s.d_scount = s.d_sstart + cb, s.d_spos0 = s.d_scount + cb, s.d_sslot = s.d_spos0 + cb;
 		s.cap_seqs = cb;
 	}
 	if (W > s.cap_want) {
@@ -373,6 +383,10 @@ struct GemmExtra {
 	int split = 0;               // columns from here on leave as relu(.)^2 in the activation type to Y2
 	void* Y2 = nullptr;
 	long ldy2 = 0;
+	const float* rs = nullptr;   // a factor per row on the accumulator: rs[(rs_idx ? rs_idx[row] : row) * rs_ld], through a sigmoid when rs_act
+	const int* rs_idx = nullptr;
+	long rs_ld = 1;
+	int rs_act = 0;
 };
 void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, long wbs, void* Y, long ldy, long ybs, int N, int M, int K, int batch, int epi,
           const SeqNorm* nrm = nullptr, int kind_as = -1, bool w_immutable = true, const GemmExtra* ex = nullptr) {
@@ -380,6 +394,7 @@ void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, lo
 	const GemmExtra none;
 	if (!ex) ex = &none;
 	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows, a.epi_f = ex->epi_f, a.split = ex->split, a.Y2 = ex->Y2, a.ldy2 = ex->ldy2, a.out_scale = ex->out_scale;
+	a.rs = ex->rs, a.rs_idx = ex->rs_idx, a.rs_ld = ex->rs_ld, a.rs_act = ex->rs_act;
 	a.w_immutable = w_immutable;
 	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
 	a.N = N, a.M = M, a.K = K, a.epi = epi;
@@ -520,10 +535,10 @@ void attention_products(Seq& s, int kind, const AttArgs& a, bf16* out, const Seq
 	}
 }
 
-void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, double kv_rows, int longest) {
+void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, double kv_rows, int longest, bool products_ok = true) {
 	a.skip = nullptr;
 	bool rest = true;
-	if (!s.m.exact && s.attn_products && s.n_on_products > 0) {
+	if (!s.m.exact && s.attn_products && products_ok && s.n_on_products > 0) {
 		const size_t n = (size_t)sb.N * a.heads * a.kd;
 		run_kernel(s, KD_ELEMENT, n * 6.0, 0, [&] { launch_k(s, k_seq_cast_cols<bf16>, cdiv(n, 256), 256, 0, (bf16*)s.a3, a.q, a.heads * a.kd, 0, a.heads * a.kd, sb.N); });
 		for (int b = 0; b < sb.B; ++b)
@@ -576,7 +591,17 @@ struct OutEpi {
 	const SeqHyper* hc = nullptr; // hyper blocks: the routed feed-forward writes the streams itself (its weighted sum is formed in that kernel)
 	const void* next_in = nullptr;      // ... and in the same kernel reads them for the sublayer that follows: its `in` weights and its norm
 	const SeqNorm* next_norm = nullptr;
+	const SeqNorm* post = nullptr;      // post-norm blocks: the norm the routed feed-forward's sum goes through on its way into the stream
 };
+// post-norm blocks: x += norm(y), y = base + the routed experts' sum; the new rows also leave in the activation type (hA), the next sublayer's input
+template <typename AT>
+void post_norm(Seq& s, const float* base, const HcMoe& moe, const SeqNorm& nm, int N) {
+	const int W = s.m.width;
+	run_kernel(s, KD_NORM, (double)N * W * (8.0 + (base ? 4 : 0) + (moe.y ? 4.0 * moe.top : 0) + act_size(s)), 0, [&] {
+		const int threads = std::min(256, std::max(32, cdiv(W, 4 * 32) * 32));
+		launch_k(s, k_seq_post_norm<AT>, N, threads, 0, s.x, (AT*)s.hA, base, moe, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, N, W);
+	});
+}
 // write the streams from a sublayer's output; with next_in / next_norm also the normed input of the sublayer that follows (into hA)
 template <typename AT>
 void hc_write(Seq& s, const SeqHyper& hc, const float* base, const HcMoe& moe, int N, const void* next_in, const SeqNorm* next_norm) {
@@ -593,9 +618,9 @@ void hc_write(Seq& s, const SeqHyper& hc, const float* base, const HcMoe& moe, i
 	});
 }
 template <typename AT>
-void out_product(Seq& s, const AT* X, const void* Wt, int N, int K, const OutEpi& oe) {
+void out_product(Seq& s, const AT* X, const void* Wt, int N, int K, const OutEpi& oe, const void* bias = nullptr) {
 	GemmExtra gx;
-	gx.res = oe.res, gx.out_scale = oe.scale;
+	gx.res = oe.res, gx.out_scale = oe.scale, gx.bias = bias; // the factor applies to product + bias
 	gemm(s, X, K, 0, Wt, K, 0, oe.dst, s.m.width, 0, N, s.m.width, K, 1, oe.epi, oe.nrm, -1, true, &gx);
 }
 
@@ -648,7 +673,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		a.scale = L.scale, a.sink = nullptr, a.gate = s.proj + Rq + Rk, a.ldg = P, a.ghs = 1, a.ges = 0, a.keep_first = 0;
 		attention(s, KD_ATTN_LATENT, a, a1, sb, kv_rows, longest);
 		gemm(s, a1, (long)H * Rk, Rk, L.w_uv, Rk, (long)Dv * Rk, a2, (long)H * Dv, Dv, N, Dv, Rk, H, EPI_ACT);
-		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe, L.b_o);
 	} else if (L.type == SEQ_DELTA) {
 		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
 		const int cq = 0, ck = G * D, cv = 2 * G * D, cb = cv + H * Dv, ca1 = cb + H, cg1 = ca1 + L.a_rank;
@@ -679,22 +704,24 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		});
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0,
 		           [&] { launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.f[4], H * Dv, (const bf16*)L.out_norm, N, H, Dv, s.m.eps, 0); });
-		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe, L.b_o);
 	} else if (L.type == SEQ_GQA) {
 		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
 		QkArgs qa;
 		qa.proj = s.proj, qa.ldp = P, qa.heads = H, qa.kv_heads = G, qa.dim = D, qa.vdim = Dv, qa.qw = (const bf16*)L.q_norm, qa.kw = (const bf16*)L.k_norm, qa.eps = s.m.eps;
-		qa.rot_dims = L.rot_dims, qa.freq = s.rot_freq[r.layer], qa.mag = s.rot_mag[r.layer], qa.q = s.f[0], qa.kc = r.cache_a, qa.vc = r.cache_b;
-		qa.v_norm = L.v_norm;
-		run_kernel(s, KD_QK, (double)N * (H * D + G * D + G * Dv) * 8, 0, [&] { launch_k(s, k_seq_qk_rope, N, 256, (size_t)std::max(L.rot_dims, 1) * sizeof(float), qa, sb); });
+		const auto rt = s.rot.find(&L);
+		qa.rot_dims = rt == s.rot.end() ? 0 : L.rot_dims, qa.freq = rt == s.rot.end() ? nullptr : rt->second.first, qa.mag = rt == s.rot.end() ? 1.f : rt->second.second, qa.q = s.f[0], qa.kc = r.cache_a, qa.vc = r.cache_b;
+		qa.v_norm = L.v_norm, qa.per_head = L.qk_per_head;
+		const size_t qk_smem = ((size_t)2 * std::max(L.rot_dims / 2, 1) + H + G) * sizeof(float);
+		run_kernel(s, KD_QK, (double)N * (H * D + G * D + G * Dv) * 8, 0, [&] { launch_k(s, k_seq_qk_rope, N, 256, qk_smem, qa, sb); });
 		AttArgs a;
 		a.q = s.f[0], a.kc = r.cache_a, a.vc = r.cache_b, a.kld = G * D, a.vld = G * Dv, a.heads = H, a.group = H / G, a.tile = attn_tile(H / G, D, Dv), a.kd = D, a.vd = Dv;
 		a.window = L.window, a.keep_first = L.window > 0 ? L.keep_first : 0, a.scale = L.scale, a.sink = nullptr;
-		a.gate = L.no_gate ? nullptr : s.proj + H * D + G * D + G * Dv, a.ldg = P, a.ghs = Dv, a.ges = 1; // a sigmoid gate per output channel, from the same stacked projection
+		a.gate = L.no_gate ? nullptr : s.proj + H * D + G * D + G * Dv, a.ldg = P, a.ghs = L.gate_per_head ? 1 : Dv, a.ges = L.gate_per_head ? 0 : 1; // a sigmoid gate per output channel (or per head), from the same stacked projection
 		a.chunk = L.chunk, a.slopes = L.dist_bias ? r.slopes : nullptr, a.add_one = L.add_one;
 		const int span = attn_span(L);
-		attention(s, KD_ATTN_WINDOW, a, a2, sb, span > 0 ? std::min(kv_rows, (double)N * span) : kv_rows, longest);
-		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+		attention(s, KD_ATTN_WINDOW, a, a2, sb, span > 0 ? std::min(kv_rows, (double)N * span) : kv_rows, longest, !L.scores_f32);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe, L.b_o);
 	} else if (L.type == SEQ_PAIR) {
 		// two mixers on the same normed input: the first one's product lands scaled in the destination, the second one's is added scaled
 		if (oe.epi != EPI_F32) CALM_FATAL("seq: a pair writes its sum to a buffer of its own");
@@ -740,7 +767,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		gla_launch(s, g, sb, ldl);
 		const long units = (long)N * (H * Dv / lo.unit);
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0, [&] { launch_k(s, k_seq_lin_out<AT>, cdiv(units, 4), 128, 0, a2, lo, N); });
-		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe, L.b_o);
 	} else if (L.type == SEQ_GLA) {
 		const int H = L.heads, D = L.dim, Dv = L.vdim;
 		const int cq = 0, ck = H * D, cv = 2 * H * D, cg = cv + H * Dv, ca1 = cg + H * Dv;
@@ -757,7 +784,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0, [&] {
 			launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.proj + cg, P, (const bf16*)L.out_norm, N, H, Dv, s.m.eps, 1);
 		});
-		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe, L.b_o);
 	} else {
 		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
 		ConvArgs ca;
@@ -769,7 +796,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		a.q = s.f[0], a.kc = r.cache_a, a.vc = r.cache_b, a.kld = G * D, a.vld = G * Dv, a.heads = H, a.group = H / G, a.tile = attn_tile(H / G, D, Dv), a.kd = D, a.vd = Dv;
 		a.window = L.window, a.scale = L.scale, a.sink = (const bf16*)L.sink, a.gate = nullptr, a.ldg = 0, a.ghs = 1, a.ges = 0, a.keep_first = 0;
 		attention(s, KD_ATTN_WINDOW, a, a2, sb, L.window > 0 ? std::min(kv_rows, (double)N * L.window) : kv_rows, longest);
-		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe, L.b_o);
 	}
 }
 
@@ -782,6 +809,11 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		gemm(s, hA, W, 0, L.w_gate_up, W, 0, s.proj, 2L * L.ff, 0, N, 2 * L.ff, W, 1, EPI_F32);
 		run_kernel(s, KD_ELEMENT, (double)N * L.ff * (8 + sizeof(AT)), 0,
 		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * L.ff, 256), 256, 0, a2, s.proj, L.ff, N, L.limit, 0, 2 * L.ff); });
+		out_product<AT>(s, a2, L.w_down, N, L.ff, oe);
+	} else if (L.ff_kind == SEQ_FF_GATED) {
+		gemm(s, hA, W, 0, L.w_gate_up, W, 0, s.proj, 2L * L.ff, 0, N, 2 * L.ff, W, 1, EPI_F32);
+		run_kernel(s, KD_ELEMENT, (double)N * L.ff * (8 + sizeof(AT)), 0,
+		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * L.ff, 256), 256, 0, a2, s.proj, L.ff, N, 0.f, L.ff_act == SEQ_ACT_GELU_TANH ? 2 : 1, 2 * L.ff); });
 		out_product<AT>(s, a2, L.w_down, N, L.ff, oe);
 	} else if (L.ff_kind == SEQ_FF_RELU2) {
 		if (L.in_tail > 0) { // the up rows rode in the mixer's input product
@@ -796,7 +828,19 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		const float* logits = s.proj;
 		int ldl = Et;
 		const int sf = L.shared_ff, ldsh = 2 * sf + (L.w_router ? 0 : Et);
-		if (L.in_tail > 0) logits = s.proj + in_rows(L), ldl = proj_stride(L); // the router's rows rode in the mixer's input product
+		const bool r2 = L.expert_act == 1;
+		// relu^2 units: the shared unit's first product is [gate row | router rows | up rows]; the up rows leave its epilogue as relu(.)^2 in the
+		// activation type, the gate's and the router's columns stay fp32
+		const int shc = (L.shared_gate ? 1 : 0) + (L.w_router ? 0 : Et);
+		if (r2 && sf > 0) {
+			GemmExtra sx;
+			if (shc > 0) {
+				sx.split = shc, sx.Y2 = a2, sx.ldy2 = sf;
+				gemm(s, hA, W, 0, L.w_sh_gate_up, W, 0, s.fsh, shc, 0, N, shc + sf, W, 1, EPI_F32, nullptr, -1, true, &sx);
+			} else gemm(s, hA, W, 0, L.w_sh_gate_up, W, 0, a2, sf, 0, N, sf, W, 1, EPI_ACT_RELU2);
+		}
+		if (r2 && sf > 0 && !L.w_router) logits = s.fsh + (L.shared_gate ? 1 : 0), ldl = shc;
+		else if (L.in_tail > 0) logits = s.proj + in_rows(L), ldl = proj_stride(L); // the router's rows rode in the mixer's input product
 		else if (!L.w_router) { // the router's rows ride behind the shared unit's [gate | up]: one product for everything that reads the normed input
 			gemm(s, hA, W, 0, L.w_sh_gate_up, W, 0, s.fsh, ldsh, 0, N, ldsh, W, 1, EPI_F32);
 			logits = s.fsh + 2 * sf, ldl = ldsh;
@@ -820,6 +864,22 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		           [&] { launch_k(s, k_seq_moe_gather<AT>, cdiv((long)pairs * W, 256), 256, 0, (AT*)s.moe_x, hA, s.moe_perm, top, pairs, W); });
 		GemmExtra gx;
 		gx.seg = s.moe_seg, gx.x_rows = pairs;
+		if (r2) {
+			// relu^2 experts: relu(w u)^2 leaves the grouped up product's epilogue (w = the pair's weight when it multiplies the expert's input: the
+			// up projection is linear, so w h becomes w u in fp32), then the grouped down product; the shared unit's down product takes the
+			// sigmoid of its gate column as a factor per row
+			GemmExtra ux = gx;
+			if (L.weight_input) ux.rs = s.moe_wt, ux.rs_idx = s.moe_perm;
+			gemm(s, s.moe_x, W, 0, L.w_gate_up, W, (long)ff * W, s.moe_a, ff, 0, N, ff, W, E, EPI_ACT_RELU2, nullptr, -1, true, &ux);
+			gemm(s, s.moe_a, ff, 0, L.w_down, ff, (long)W * ff, s.moe_d, W, 0, N, W, ff, E, EPI_F32, nullptr, -1, true, &gx);
+			if (sf > 0) {
+				GemmExtra dx;
+				if (L.shared_gate) dx.rs = s.fsh, dx.rs_ld = shc, dx.rs_act = 1;
+				gemm(s, a2, sf, 0, L.w_sh_down, sf, 0, s.mo, W, 0, N, W, sf, 1, EPI_F32, nullptr, -1, true, &dx);
+			}
+			post_norm<AT>(s, sf > 0 ? s.mo : nullptr, HcMoe{s.moe_d, s.moe_inv, s.moe_sel, L.weight_input ? nullptr : s.moe_wt, top, E}, *oe.post, N);
+			return;
+		}
 		gemm(s, s.moe_x, W, 0, L.w_gate_up, W, 2L * ff * W, s.moe_y, 2L * ff, 0, N, 2 * ff, W, E, EPI_F32, nullptr, -1, true, &gx);
 		if (oe.hc) {
 			// hyper blocks: the shared unit's product is the base of y, the routed sum is formed while the streams are written; the two units'
@@ -840,6 +900,10 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		run_kernel(s, KD_ELEMENT, (double)pairs * ff * (8 + sizeof(AT)), 0,
 		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)pairs * ff, 256), 256, 0, (AT*)s.moe_a, s.moe_y, ff, pairs, 0.f, 1, 2 * ff); });
 		gemm(s, s.moe_a, ff, 0, L.w_down, ff, (long)W * ff, s.moe_d, W, 0, N, W, ff, E, EPI_F32, nullptr, -1, true, &gx);
+		if (oe.post) { // post-norm blocks: the weighted sum is formed by the kernel that norms it and adds it to the stream
+			post_norm<AT>(s, nullptr, HcMoe{s.moe_d, s.moe_inv, s.moe_sel, s.moe_wt, top, E}, *oe.post, N);
+			return;
+		}
 		run_kernel(s, KD_ELEMENT, (double)N * W * (8 + 4.0 * top) + (oe.res ? (double)N * W * 4 : 0), 0, [&] {
 			launch_k(s, k_seq_moe_combine<AT>, cdiv((long)N * W, 256), 256, 0, oe.dst, oe.res, s.moe_d, s.moe_inv, s.moe_wt, top, N, W, s.moe_sel, E, (const AT*)hA, 0);
 		});
@@ -868,6 +932,24 @@ void layer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		s.h_ready = next != nullptr;
 		return;
 	}
+	if (s.m.block == SEQ_BLOCK_POST) {
+		// the sublayers read the stream itself: hA holds its rows in the activation type, written by the kernel that last changed them
+		const HcMoe none{nullptr, nullptr, nullptr, nullptr, 0, 0};
+		if (!s.h_ready) {
+			const size_t n = (size_t)N * s.m.width;
+			run_kernel(s, KD_ELEMENT, n * (4.0 + sizeof(AT)), 0, [&] { launch_k(s, k_seq_cast_cols<AT>, cdiv(n, 256), 256, 0, (AT*)s.hA, s.x, s.m.width, 0, s.m.width, N); });
+			s.h_ready = true;
+		}
+		mixer_typed<AT>(s, L, r, sb, kv_rows, longest, OutEpi{EPI_F32, nullptr, s.mo, nullptr});
+		post_norm<AT>(s, s.mo, none, L.norm1, N);
+		if (L.ff > 0) {
+			OutEpi oe{EPI_F32, nullptr, s.mo, nullptr};
+			oe.post = &L.norm2;
+			feed_forward<AT>(s, L, sb, oe);
+			if (L.ff_kind != SEQ_FF_MOE) post_norm<AT>(s, s.mo, none, L.norm2, N);
+		}
+		return;
+	}
 	norm(s, s.hA, s.x, nullptr, L.norm1, N);
 	if (s.m.block == SEQ_BLOCK_SERIAL) {
 		mixer_typed<AT>(s, L, r, sb, kv_rows, longest, OutEpi{EPI_DYT_RES, &L.norm1b, s.x, nullptr});
@@ -889,8 +971,9 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 	const int N = sb.N;
 	const bool looped = m.loop_times > 1;
 	s.h_ready = false;
-	run_kernel(s, KD_EMBED, (double)N * m.width * (2.0 + (m.pos_table ? 2.0 : 0.0) + 4.0 * s.streams + (looped ? 4.0 : 0.0)), 0,
-	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width, m.embed_scale != 0.f ? m.embed_scale : 1.f, (const bf16*)m.pos_table, s.d_tpos, s.streams); });
+	run_kernel(s, KD_EMBED, (double)N * m.width * (2.0 + (m.pos_table ? 2.0 : 0.0) + (m.bigram ? 2.0 : 0.0) + 4.0 * s.streams + (looped ? 4.0 : 0.0)), 0,
+	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width, m.embed_scale != 0.f ? m.embed_scale : 1.f, (const bf16*)m.pos_table, s.d_tpos, s.streams,
+	                          EmbedBigram{(const bf16*)m.bigram, s.d_tprev, m.bigram_buckets, m.bigram_mul_prev, m.bigram_mul_cur}); });
 	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
 		RunState& r = s.runs[ri];
 		const SeqLayer& L = s.layers[r.layer];
@@ -910,7 +993,9 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 	if (n_want) {
 		if (m.block == SEQ_BLOCK_HYPER) hc_read(s, s.hW, s.d_want, nullptr, m.final_norm, n_want);
 		else norm(s, s.hW, s.x, s.d_want, m.final_norm, n_want);
-		gemm(s, s.hW, m.width, 0, m.head, m.width, 0, s.logits, m.vocab, 0, n_want, m.vocab, m.width, 1, EPI_F32);
+		GemmExtra lx;
+		lx.out_scale = m.logit_scale != 1.f ? m.logit_scale : 0.f; // 0: no factor
+		gemm(s, s.hW, m.width, 0, m.head, m.width, 0, s.logits, m.vocab, 0, n_want, m.vocab, m.width, 1, EPI_F32, nullptr, -1, true, &lx);
 	}
 }
 
@@ -1060,12 +1145,15 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 	CUDA_CHECK(cudaFuncSetAttribute(k_seq_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
 	CUDA_CHECK(cudaFuncSetAttribute(k_seq_attention<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
 	// rotation tables of the grouped-query attentions: angle step per rotated pair (in double), rescaled between two wavelengths
-	s.rot_freq.assign(m.n_layers, nullptr), s.rot_mag.assign(m.n_layers, 1.f);
-	for (int i = 0; i < m.n_layers; ++i) {
-		const SeqLayer& L = s.layers[i];
-		if (L.type != SEQ_GQA || L.rot_dims < 2) continue;
+	std::function<void(const SeqLayer&)> rot_table = [&](const SeqLayer& L) {
+		if (L.type == SEQ_PAIR) {
+			rot_table(L.pair[0]), rot_table(L.pair[1]);
+			return;
+		}
+		if (L.type != SEQ_GQA || L.rot_dims < 2) return;
 		const int dims = L.rot_dims, half = dims / 2;
 		std::vector<double> f(half);
+		float mag = 1.f;
 		for (int j = 0; j < half; ++j) f[j] = pow((double)L.rot_base, -2.0 * j / dims);
 		if (L.rot_factor > 0.f) {
 			// the pair whose wavelength fits `t` times into the original context: pairs below `lo` keep their step, pairs above `hi`
@@ -1076,11 +1164,13 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 				const double ramp = std::min(1.0, std::max(0.0, (j - lo) / std::max(hi - lo, 0.001)));
 				f[j] = f[j] / L.rot_factor * ramp + f[j] * (1.0 - ramp);
 			}
-			s.rot_mag[i] = (float)(0.1 * log((double)L.rot_factor) + 1.0);
+			mag = (float)(0.1 * log((double)L.rot_factor) + 1.0);
 		}
-		s.rot_freq[i] = (double*)dalloc(half * sizeof(double));
-		CUDA_CHECK(cudaMemcpy(s.rot_freq[i], f.data(), half * sizeof(double), cudaMemcpyHostToDevice));
-	}
+		double* dev = (double*)dalloc(half * sizeof(double));
+		CUDA_CHECK(cudaMemcpy(dev, f.data(), half * sizeof(double), cudaMemcpyHostToDevice));
+		s.rot[&L] = std::make_pair(dev, mag);
+	};
+	for (const SeqLayer& L : s.layers) rot_table(L);
 	// workspace widths
 	std::function<void(const SeqLayer&)> widths = [&](const SeqLayer& L) {
 		if (L.type == SEQ_PAIR) {
@@ -1090,7 +1180,7 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 		if (L.ff > 0 && L.ff_kind == SEQ_FF_MOE) {
 			s.max_top = std::max(s.max_top, L.top), s.max_experts = std::max(s.max_experts, L.experts + L.ident), s.w_moe_ff = std::max(s.w_moe_ff, (size_t)L.ff);
 			s.w_proj = std::max(s.w_proj, (size_t)L.experts + L.ident);
-			if (L.shared_ff > 0) s.w_fsh = std::max(s.w_fsh, (size_t)2 * L.shared_ff + L.experts + L.ident);
+			if (L.shared_ff > 0) s.w_fsh = std::max(s.w_fsh, (size_t)2 * L.shared_ff + 1 + L.experts + L.ident);
 			s.w_a = std::max(s.w_a, (size_t)L.shared_ff);
 		}
 		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim}); // a3 holds the queries
@@ -1133,7 +1223,7 @@ extern "C" void calm_b200_seq_release(void* handle) {
 	cudaFree(s->table_dev), cudaFree(s->d_tok), cudaFree(s->d_want), cudaFree(s->d_argmax), cudaFree(s->logits), cudaFree(s->hW);
 	cudaFree(s->part), cudaFree(s->a3), cudaFree(s->att_kb), cudaFree(s->att_vt), cudaFree(s->att_s), cudaFree(s->att_p), cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
 	for (float* p : s->f) cudaFree(p);
-	for (double* p : s->rot_freq) cudaFree(p);
+	for (auto& kv : s->rot) cudaFree(kv.second.first);
 	cudaFree(s->ah), cudaFree(s->mo), cudaFree(s->moe_sel), cudaFree(s->moe_wt), cudaFree(s->moe_y), cudaFree(s->moe_d), cudaFree(s->moe_x), cudaFree(s->moe_a);
 	for (cudaEvent_t e : s->ev) cudaEventDestroy(e);
 	for (cudaEvent_t e : s->timer) cudaEventDestroy(e);
@@ -1145,7 +1235,7 @@ extern "C" int calm_b200_seq_open(void* handle) {
 	Seq& s = *(Seq*)handle;
 	for (int i = 0; i < (int)s.slots.size(); ++i)
 		if (!s.slots[i].open) {
-			s.slots[i].open = true, s.slots[i].len = 0, s.slots[i].pages.clear();
+			s.slots[i].open = true, s.slots[i].len = 0, s.slots[i].last_tok = -1, s.slots[i].pages.clear();
 			std::function<void(RunState&)> zero = [&](RunState& r) { // a slot that is used again starts from zero state
 				if (r.conv_per_slot) CUDA_CHECK(cudaMemsetAsync(r.conv + r.conv_per_slot * i, 0, r.conv_per_slot * sizeof(float), s.stream));
 				if (r.delta_per_slot) CUDA_CHECK(cudaMemsetAsync(r.delta + r.delta_per_slot * i, 0, r.delta_per_slot * sizeof(float), s.stream));
@@ -1196,8 +1286,8 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 	// pages for the new tokens, then the batch description
 	double kv_rows = 0; // cache rows the causal attentions read this step
 	int longest = 0;    // longest sequence after this step
-	s.h_meta.resize((size_t)5 * N + 4 * n_seq);
-	int *tok = s.h_meta.data(), *tslot = tok + N, *tpos = tslot + N, *tfirst = tpos + N, *skip = tfirst + N, *sstart = skip + N, *scount = sstart + n_seq, *spos0 = scount + n_seq,
+	s.h_meta.resize((size_t)6 * N + 4 * n_seq);
+	int *tok = s.h_meta.data(), *tslot = tok + N, *tpos = tslot + N, *tfirst = tpos + N, *skip = tfirst + N, *tprev = skip + N, *sstart = tprev + N, *scount = sstart + n_seq, *spos0 = scount + n_seq,
 	    *sslot = spos0 + n_seq;
 	int at = 0;
 	s.hb_start.resize(n_seq), s.hb_count.resize(n_seq), s.hb_pos0.resize(n_seq), s.hb_slot.resize(n_seq);
@@ -1214,10 +1304,10 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 			CUDA_CHECK(cudaMemcpyAsync(s.table_dev + o, s.table.data() + o, (sl.pages.size() - had) * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 		}
 		sstart[b] = at, scount[b] = counts[b], spos0[b] = sl.len, sslot[b] = slots[b];
-		for (int t = 0; t < counts[b]; ++t, ++at) tok[at] = tokens[at], tslot[at] = slots[b], tpos[at] = sl.len + t, tfirst[at] = sstart[b], skip[at] = counts[b] >= kAttnGemmMin, kv_rows += sl.len + t + 1;
+		for (int t = 0; t < counts[b]; ++t, ++at) tprev[at] = t ? tokens[at - 1] : sl.last_tok, tok[at] = tokens[at], tslot[at] = slots[b], tpos[at] = sl.len + t, tfirst[at] = sstart[b], skip[at] = counts[b] >= kAttnGemmMin, kv_rows += sl.len + t + 1;
 		s.hb_start[b] = sstart[b], s.hb_count[b] = counts[b], s.hb_pos0[b] = sl.len, s.hb_slot[b] = slots[b];
 		if (counts[b] >= kAttnGemmMin) ++s.n_on_products, s.tok_on_products += counts[b];
-		sl.len += counts[b];
+		sl.len += counts[b], sl.last_tok = tokens[at - 1];
 		longest = std::max(longest, sl.len);
 	}
 	CUDA_CHECK(cudaMemcpyAsync(s.d_tok, tok, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
@@ -1225,6 +1315,7 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 	CUDA_CHECK(cudaMemcpyAsync(s.d_tpos, tpos, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_tfirst, tfirst, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_skip, skip, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	if (m.bigram) CUDA_CHECK(cudaMemcpyAsync(s.d_tprev, tprev, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_sstart, sstart, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_scount, scount, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_spos0, spos0, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));

@@ -17,11 +17,12 @@ def register(architecture: str, loader: Callable) -> None:
 
 
 def _defaults() -> None:
-    from . import bovinex, vimulorn, zazilix
+    from . import bovinex, sopepel, vimulorn, zazilix
 
     register(vimulorn.ARCHITECTURE, vimulorn.load)
     register(bovinex.ARCHITECTURE, bovinex.load)
     register(zazilix.ARCHITECTURE, zazilix.load)
+    register(sopepel.ARCHITECTURE, sopepel.load)
 
 
 def architecture_of(path: str) -> str:

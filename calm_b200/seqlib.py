@@ -13,8 +13,9 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 SEQ_LATENT, SEQ_DELTA, SEQ_WINDOW, SEQ_GQA, SEQ_GLA, SEQ_MLSTM, SEQ_HGRN2, SEQ_MAMBA2, SEQ_PAIR = 0, 1, 2, 3, 4, 5, 6, 7, 8
 NORM_DYT, NORM_RMS = 0, 1
-BLOCK_SERIAL, BLOCK_PARALLEL, BLOCK_HYPER = 0, 1, 2
-FF_CLAMPED, FF_RELU2, FF_MOE = 0, 1, 2
+BLOCK_SERIAL, BLOCK_PARALLEL, BLOCK_HYPER, BLOCK_POST = 0, 1, 2, 3
+FF_CLAMPED, FF_RELU2, FF_MOE, FF_GATED = 0, 1, 2, 3
+ACT_SILU, ACT_GELU_TANH = 0, 1
 _fptr = C.POINTER(C.c_float)
 _iptr = C.POINTER(C.c_int)
 
@@ -42,7 +43,9 @@ SeqLayer._fields_ = [(n, C.c_int) for n in ("type", "heads", "kv_heads", "dim", 
                [(n, C.c_void_p) for n in ("lower", "conv_b", "skip_d")] + [("norm_groups", C.c_int), ("pair", C.POINTER(SeqLayer)), ("pair_scale", C.c_float * 2),
                                                                          ("hc1", SeqHyper), ("hc2", SeqHyper), ("route_mode", C.c_int), ("ident", C.c_int),
                                                                          ("route_scale", C.c_float), ("correction", C.c_void_p), ("shared_ff", C.c_int),
-                                                                         ("w_sh_gate_up", C.c_void_p), ("w_sh_down", C.c_void_p)]
+                                                                         ("w_sh_gate_up", C.c_void_p), ("w_sh_down", C.c_void_p),
+                                                                         ("qk_per_head", C.c_int), ("gate_per_head", C.c_int), ("b_o", C.c_void_p), ("scores_f32", C.c_int), ("ff_act", C.c_int),
+                                                                         ("expert_act", C.c_int), ("weight_input", C.c_int), ("shared_gate", C.c_int)]
 
 
 class SeqModel(C.Structure):
@@ -50,7 +53,8 @@ class SeqModel(C.Structure):
                [(n, C.c_int) for n in ("exact", "max_tokens", "max_seqs", "page")] + \
                [("embed", C.c_void_p), ("head", C.c_void_p), ("final_norm", SeqNorm), ("layers", C.POINTER(SeqLayer)),
                 ("norm_kind", C.c_int), ("norm_offset", C.c_float), ("block", C.c_int), ("embed_scale", C.c_float),
-                ("streams", C.c_int), ("norm_scalar", C.c_int), ("pos_table", C.c_void_p), ("max_positions", C.c_int)]
+                ("streams", C.c_int), ("norm_scalar", C.c_int), ("pos_table", C.c_void_p), ("max_positions", C.c_int),
+                ("bigram", C.c_void_p), ("bigram_buckets", C.c_int), ("bigram_mul_prev", C.c_int), ("bigram_mul_cur", C.c_int), ("logit_scale", C.c_float)]
 
 
 _lib = None
@@ -96,7 +100,7 @@ class SeqError(RuntimeError):
 
 class SeqDeviceModel:
     """A layer-list model on the GPU.  `layers` are dicts of SeqLayer fields whose tensor-valued entries name tensors in
-    `tensors` (host torch tensors, uploaded here); vimulorn.py and bovinex.py are the hosts that fill them from a checkpoint."""
+    `tensors` (host torch tensors, uploaded here); vimulorn.py, bovinex.py, zazilix.py and sopepel.py are the hosts that fill them from a checkpoint."""
 
     def __init__(self, head: Dict[str, object], layers: List[Dict[str, object]], tensors: Dict[str, "object"], exact: bool = False,
                  max_tokens: int = 4096, max_seqs: int = 64, page: int = 16):
@@ -147,6 +151,9 @@ class SeqDeviceModel:
         m.block, m.embed_scale = int(head.get("block", BLOCK_SERIAL)), float(head.get("embed_scale", 1.0))
         m.streams, m.norm_scalar = int(head.get("streams", 1)), int(head.get("norm_scalar", 0))
         m.pos_table, m.max_positions = ptr(head.get("pos_table")), int(head.get("max_positions", 0))
+        m.bigram, m.bigram_buckets = ptr(head.get("bigram")), int(head.get("bigram_buckets", 0))
+        m.bigram_mul_prev, m.bigram_mul_cur = int(head.get("bigram_mul_prev", 0)), int(head.get("bigram_mul_cur", 0))
+        m.logit_scale = float(head.get("logit_scale", 1.0))
         m.layers = C.cast(self._layers, C.POINTER(SeqLayer))
         self.desc = m
         self.vocab, self.width = m.vocab, m.width

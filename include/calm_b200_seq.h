@@ -46,6 +46,20 @@
  * the choice made on score + correction, the weights score * route_scale, not renormalised).  The last `ident` router outputs are
  * identity experts (output = input); a shared unit of the same form (shared_ff) runs for every token and is added.
  * A span of layers can be run several times in a row with the same weights (loop_*), each pass with its own state.
+ *
+ * Post-norm blocks (SEQ_BLOCK_POST): a sublayer reads the residual stream itself (rounded to the activation type) and its output
+ * comes back through the model's RMS norm, x <- x + norm1(mixer(x)), then x <- x + norm2(feed-forward(x)).  Any mixer of the list
+ * runs in them, pairs included.
+ * Options of SEQ_GQA added for them: `qk_per_head` (the query / key RMS norm runs over each head's `dim` channels with one weight
+ * vector [dim] shared by the heads), `gate_per_head` (one sigmoid gate per head: `heads` gate rows in w_in), `b_o` (a bias of the
+ * output projection), `scores_f32` (scores and softmax weights are kept in fp32 also for prompts).
+ * Feed-forward SEQ_FF_GATED: down(act(gate) * up) with act = SiLU or the tanh form of GELU (ff_act).
+ * Routed experts, further options: `expert_act` 1 -- an expert (and the shared unit) is down(relu(up)^2), without gate rows;
+ * route_mode 2 -- scores are sigmoid(router output), the `top` highest are taken, the weights are those scores times route_scale,
+ * not renormalised; `weight_input` -- the weight multiplies the expert's input instead of its output; `shared_gate` -- the shared
+ * unit's output is multiplied by sigmoid(one more row of its first product), one number per token.
+ * Embedding: SeqModel.bigram adds row (previous token * mul_prev + token * mul_cur) mod buckets of a second table (row `buckets`
+ * for a sequence's first token); the previous token is kept with the sequence's slot.  SeqModel.logit_scale multiplies the logits.
  */
 #ifndef CALM_B200_SEQ_H
 #define CALM_B200_SEQ_H
@@ -59,8 +73,9 @@ extern "C" {
 
 enum SeqMixer { SEQ_LATENT = 0, SEQ_DELTA = 1, SEQ_WINDOW = 2, SEQ_GQA = 3, SEQ_GLA = 4, SEQ_MLSTM = 5, SEQ_HGRN2 = 6, SEQ_MAMBA2 = 7, SEQ_PAIR = 8 };
 enum SeqNormKind { SEQ_NORM_DYT = 0, SEQ_NORM_RMS = 1 };
-enum SeqBlock { SEQ_BLOCK_SERIAL = 0, SEQ_BLOCK_PARALLEL = 1, SEQ_BLOCK_HYPER = 2 };
-enum SeqFfKind { SEQ_FF_CLAMPED = 0, SEQ_FF_RELU2 = 1, SEQ_FF_MOE = 2 };
+enum SeqBlock { SEQ_BLOCK_SERIAL = 0, SEQ_BLOCK_PARALLEL = 1, SEQ_BLOCK_HYPER = 2, SEQ_BLOCK_POST = 3 };
+enum SeqFfKind { SEQ_FF_CLAMPED = 0, SEQ_FF_RELU2 = 1, SEQ_FF_MOE = 2, SEQ_FF_GATED = 3 };
+enum SeqFfAct { SEQ_ACT_SILU = 0, SEQ_ACT_GELU_TANH = 1 };
 
 /* a norm: bf16 weight[n]; Dynamic Tanh also bf16 bias[n], bf16 alpha[1] (device pointers; NULL for an RMS norm) */
 struct SeqNorm {
@@ -153,13 +168,25 @@ struct SeqLayer {
 	/* SEQ_BLOCK_HYPER */
 	struct SeqHyper hc1, hc2;
 	/* SEQ_FF_MOE extras */
-	int route_mode;        /* 0: softmax over the chosen logits; 1: softmax over all, choice on score + correction, weight = score * route_scale */
+	int route_mode;        /* 0: softmax over the chosen logits; 1: softmax over all, choice on score + correction, weight = score * route_scale;
+	                          2: score = sigmoid(output), choice on score, weight = score * route_scale */
 	int ident;             /* identity experts: router outputs experts .. experts + ident - 1 (w_router has experts + ident rows) */
 	float route_scale;
 	const void* correction; /* bf16 [experts + ident] or NULL */
 	int shared_ff;         /* width of the shared unit, 0: none */
 	const void* w_sh_gate_up; /* (2*shared_ff, width) rows [gate | up]; with w_router == NULL the router's experts + ident rows follow them (one product) */
 	const void* w_sh_down;    /* (width, shared_ff) */
+	/* SEQ_GQA, further options */
+	int qk_per_head;       /* 1: q_norm / k_norm are bf16 [dim], the RMS norm runs over each head's channels */
+	int gate_per_head;     /* 1: the gate rows of w_in are `heads` rows, one sigmoid gate per head */
+	const void* b_o;       /* bf16 [width]: bias of the output projection, or NULL (any mixer) */
+	int scores_f32;        /* 1: scores and softmax weights never leave fp32: prompts stay on the fused attention kernel instead of bf16 tensor-core products */
+	/* SEQ_FF_GATED */
+	int ff_act;            /* enum SeqFfAct: activation of the gate rows (w_gate_up rows [gate | up]) */
+	/* SEQ_FF_MOE, further options */
+	int expert_act;        /* 0: an expert is down(silu(gate) * up), rows [gate | up]; 1: down(relu(up)^2), w_gate_up = [experts](ff, width), the shared unit alike */
+	int weight_input;      /* 1: a choice's weight multiplies the expert's input */
+	int shared_gate;       /* 1: w_sh_gate_up has one more row behind the unit's first rows (before the router's): the shared output is multiplied by its sigmoid */
 };
 
 struct SeqModel {
@@ -182,6 +209,9 @@ struct SeqModel {
 	int norm_scalar;    /* 1: every norm weight of the model is one number (bf16 [1]) for all columns */
 	const void* pos_table; /* bf16 (max_positions, width): learned position rows added to the embedding, or NULL */
 	int max_positions;  /* rows of pos_table: no sequence grows beyond */
+	const void* bigram; /* bf16 (bigram_buckets + 1, width): rows added to the embedding, picked by a hash of (previous token, token); or NULL */
+	int bigram_buckets, bigram_mul_prev, bigram_mul_cur;
+	float logit_scale;  /* factor on the logits (0 is read as 1) */
 };
 
 /* cudaMalloc + copy, like upload_cuda */
