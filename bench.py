@@ -253,16 +253,16 @@ def main():
     ap.add_argument("--kvbits", type=int, default=16, choices=[16, 8], help="KV cache element: fp16 (what the reference uses up to 4096 positions) or e5m2 (its choice beyond, run.c:537-539)")
     ap.add_argument("--layers", type=int, default=None, help="(debug) override the layer count")
     ap.add_argument("--pos0", type=int, default=None, help="(debug) first timed position instead of the end of the context")
-    ap.add_argument("--family", default="calm", choices=["calm", "vimulorn", "bovinex", "zazilix"],
+    ap.add_argument("--family", default="calm", choices=["calm", "vimulorn", "bovinex", "zazilix", "sopepel"],
                     help="vimulorn / bovinex / zazilix: prompt / decode throughput of the layer-list runtime at a few realistic layer sizes beside the closest "
                          "existing model at equal size (vimulorn: a Llama-shaped twin on the calm engine; bovinex: vimulorn on the same runtime; zazilix: "
-                         "bovinex on the same runtime); one JSON line each; the default workload and its one JSON line are untouched")
-    ap.add_argument("--sizes", default="w1024,w2048,w4096", help="--family vimulorn / bovinex / zazilix: which sizes of calm_b200/seqbench.py to run")
-    ap.add_argument("--prompt", type=int, default=2048, help="--family vimulorn / bovinex / zazilix: prompt length")
-    ap.add_argument("--batch", type=int, default=16, help="--family vimulorn / bovinex / zazilix: sequences decoded together")
-    ap.add_argument("--no-twin", action="store_true", help="--family vimulorn / bovinex / zazilix: skip the Llama-shaped twin")
+                         "bovinex on the same runtime; sopepel: bovinex likewise); one JSON line each; the default workload and its one JSON line are untouched")
+    ap.add_argument("--sizes", default="w1024,w2048,w4096", help="--family vimulorn / bovinex / zazilix / sopepel: which sizes of calm_b200/seqbench.py to run")
+    ap.add_argument("--prompt", type=int, default=2048, help="--family vimulorn / bovinex / zazilix / sopepel: prompt length")
+    ap.add_argument("--batch", type=int, default=16, help="--family vimulorn / bovinex / zazilix / sopepel: sequences decoded together")
+    ap.add_argument("--no-twin", action="store_true", help="--family vimulorn / bovinex / zazilix / sopepel: skip the Llama-shaped twin")
     args = ap.parse_args()
-    if args.family in ("vimulorn", "bovinex", "zazilix"):
+    if args.family in ("vimulorn", "bovinex", "zazilix", "sopepel"):
         from calm_b200 import seqbench
 
         seqbench.main(args.sizes.split(","), prompt=args.prompt, batch=args.batch, steps=min(args.steps, 64), warmup=min(max(args.warmup, 3), 16), twin=not args.no_twin,

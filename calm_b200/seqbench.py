@@ -2,7 +2,8 @@
 model on the same GPU: Vimulorn beside a Llama-shaped stack of the same width, depth, head geometry and feed-forward width in
 fp16 on the calm engine; Bovinex beside Vimulorn at the same width, depth, head geometry, window and feed-forward width on
 the same runtime (both have windowed grouped-query attention and a recurrent mixer with a [dim x vdim] state per head); Zazilix
-beside Bovinex likewise (both have grouped-query attention with a bounded view, linear recurrences on the same scan kernel and routed experts).
+beside Bovinex likewise (both have grouped-query attention with a bounded view, linear recurrences on the same scan kernel and routed experts);
+Sopepel beside Bovinex too (the same two mixers, grouped-query attention and gated linear attention, side by side in every layer with half the heads each).
 
 Per size: prompt throughput (one prompt of `prompt` tokens as one step), decode throughput for one sequence and for a
 batch, each after warm-up, timed with CUDA events on the library's stream; then one profiled pass that brackets every
@@ -72,6 +73,20 @@ def zazilix_config(z: dict, max_positions: int = 4096) -> dict:
             "width": z["width"], "streams": 4, "max_positions": max_positions}
 
 
+def sopepel_config(z: dict) -> dict:
+    """Blocks of [pair + dense, pair + routed experts, pair + dense]; a pair is grouped-query attention inside blocks of `window` positions beside
+    gated linear attention, half of the size's heads each, so a layer's mixer has the width of one of Bovinex's; eight relu^2 experts of half the
+    dense width (two active per token) and a gated shared unit of a quarter of it."""
+    H, D = z["heads"], z["dim"]
+    dense = {"ff": z["ff"], "kind": "dense"}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 2}, "router": {"experts": 8, "top": 2}, "shared": {"ff": z["ff"] // 4}}
+    mixer = {"left": {"heads": H // 2, "kv_heads": max(z["kv_heads"] // 2, 1), "dim": D, "vdim": D, "scale": D ** -0.5, "rot": {"dims": D // 2, "base": 1e6}, "mask": {"size": z["window"]}},
+             "right": {"heads": H // 2, "dim": D, "vdim": D, "tau": 16.0, "a_rank": 64}, "left_scale": 1.0, "right_scale": 0.5}
+    block = [{"type": "parallel", "mixer": mixer, "mlp": dense}, {"type": "parallel", "mixer": mixer, "mlp": moe}, {"type": "parallel", "mixer": mixer, "mlp": dense}]
+    return {"architecture": "Sopepel", "embedding": {"bigram": {"buckets": 16381, "mul_prev": 36313, "mul_cur": 27191}}, "layers": block * z["blocks"], "norm": {"eps": 1e-5},
+            "vocab": z["vocab"], "width": z["width"], "logit_scale": 1.0}
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -92,10 +107,11 @@ def roofline_table(stats: dict, hbm_gbs: float, tflops: float) -> dict:
 
 
 def bench_family(family: str, name: str, prompt: int, batch: int, steps: int, warmup: int, seed: int = 0) -> list:
-    from . import bovinex, vimulorn, zazilix
+    from . import bovinex, sopepel, vimulorn, zazilix
 
     z = SIZES[name]
-    mod, cfg = {"bovinex": (bovinex, bovinex_config(z)), "zazilix": (zazilix, zazilix_config(z, prompt + steps + 2 * warmup + 64))}.get(family, (vimulorn, vimulorn_config(z)))
+    mod, cfg = {"bovinex": (bovinex, bovinex_config(z)), "zazilix": (zazilix, zazilix_config(z, prompt + steps + 2 * warmup + 64)),
+                "sopepel": (sopepel, sopepel_config(z))}.get(family, (vimulorn, vimulorn_config(z)))
     hbm, tf, src = peaks()
     t0 = time.time()
     tensors = mod.random_tensors(cfg, seed)
@@ -190,7 +206,7 @@ def main(sizes, prompt=2048, batch=16, steps=32, warmup=8, twin=True, family="vi
         lines = bench_family(family, name, prompt, batch, steps, warmup)
         if twin and family == "bovinex":
             lines += bench_family("vimulorn", name, prompt, batch, steps, warmup)
-        if twin and family == "zazilix":
+        if twin and family in ("zazilix", "sopepel"):
             lines += bench_family("bovinex", name, prompt, batch, steps, warmup)
         if llama:
             lines += bench_llama_twin(name, prompt, steps, warmup)

@@ -10,6 +10,11 @@ from typing import Dict, List
 
 import numpy as np
 
+# mechanisms a test can leave out to show that the comparison would notice
+KNOBS = {"weight_on_input": True, "shared_gate": True, "bigram": True, "norm_per_head": True, "gate_per_head": True}
+# router margins of the last forward(): per routed layer, per token, the gap between the last chosen score and the best one left out
+MARGINS: List[np.ndarray] = []
+
 
 def rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
     return x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * w
@@ -33,7 +38,7 @@ def embed(t: Dict[str, np.ndarray], bg: dict, toks: List[int]) -> np.ndarray:
     out = []
     for i, tok in enumerate(toks):
         row = B if i == 0 else (toks[i - 1] * int(bg["mul_prev"]) + tok * int(bg["mul_cur"])) % B
-        out.append(t["embed"][tok] + t["bigram"][row])
+        out.append(t["embed"][tok] + (t["bigram"][row] if KNOBS["bigram"] else 0.0))
     return np.stack(out)
 
 
@@ -65,10 +70,14 @@ def left_attention(t, m: str, mx: dict, h: np.ndarray, eps: float) -> np.ndarray
     q = (h @ t[m + "q"].T + t[m + "q.b"]).reshape(T, H, D)
     k = (h @ t[m + "k"].T + t[m + "k.b"]).reshape(T, G, D)
     v = (h @ t[m + "v"].T + t[m + "v.b"]).reshape(T, G, Dv)
-    q, k = rms_norm(q, t[m + "q.norm"], eps), rms_norm(k, t[m + "k.norm"], eps)
+    if KNOBS["norm_per_head"]:
+        q, k = rms_norm(q, t[m + "q.norm"], eps), rms_norm(k, t[m + "k.norm"], eps)
+    else:  # (a wrong reading: one norm over all heads)
+        q = rms_norm(q.reshape(T, -1), np.tile(t[m + "q.norm"], H), eps).reshape(T, H, D)
+        k = rms_norm(k.reshape(T, -1), np.tile(t[m + "k.norm"], G), eps).reshape(T, G, D)
     q, k = rotate(q, mx.get("rot")), rotate(k, mx.get("rot"))
     size = int((mx.get("mask") or {}).get("size", 0))
-    gate = sigmoid(h @ t[m + "g"].T)  # [T, H]
+    gate = sigmoid(h @ t[m + "g"].T) if KNOBS["gate_per_head"] else np.ones((T, H))  # [T, H]
     out = np.zeros((T, H, Dv))
     for i in range(T):
         js = [j for j in range(i + 1) if sees(i, j, size)]
@@ -116,7 +125,10 @@ def small_unit(t, f: str, h: np.ndarray) -> np.ndarray:
 def route(z: np.ndarray, top: int):
     """per token: the `top` experts with the largest sigmoid scores (lowest index wins a tie), weights = those scores"""
     s = sigmoid(z)
-    order = np.argsort(-s, axis=-1, kind="stable")[:, :top]
+    full = np.argsort(-s, axis=-1, kind="stable")
+    order = full[:, :top]
+    if top < s.shape[-1]:
+        MARGINS.append(np.take_along_axis(s, full[:, top - 1:top], -1)[:, 0] - np.take_along_axis(s, full[:, top:top + 1], -1)[:, 0])
     return order, np.take_along_axis(s, order, -1)
 
 
@@ -126,9 +138,12 @@ def experts(t, f: str, ml: dict, h: np.ndarray) -> np.ndarray:
     out = np.zeros_like(h)
     for n in range(h.shape[0]):
         for e, w in zip(sel[n], wt[n]):
-            out[n] += small_unit(t, f + f"e{e}.", (w * h[n])[None])[0]  # the weight multiplies the expert's input
+            if KNOBS["weight_on_input"]:
+                out[n] += small_unit(t, f + f"e{e}.", (w * h[n])[None])[0]  # the weight multiplies the expert's input
+            else:
+                out[n] += w * small_unit(t, f + f"e{e}.", h[n][None])[0]
     if ml.get("shared"):
-        out += sigmoid(h @ t[f + "shared.sg"].T) * small_unit(t, f + "shared.", h)
+        out += (sigmoid(h @ t[f + "shared.sg"].T) if KNOBS["shared_gate"] else 1.0) * small_unit(t, f + "shared.", h)
     assert E == t[f + "router"].shape[0]
     return out
 
