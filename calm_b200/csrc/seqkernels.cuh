@@ -165,6 +165,19 @@ __global__ void k_seq_cast_cols(AT* out, const float* src, int lds, int col, int
 	out[i] = to_act<AT>(src[(i / len) * lds + col + i % len]);
 }
 
+// queries for the product path with fp32-accurate scores: per (token, head) the row [hi | hi | lo] of bf16 values, hi = bf16(q), lo = bf16(q - hi);
+// against key rows [hi | lo | hi] one product of depth 3 kd sums q_hi k_hi + q_hi k_lo + q_lo k_hi in fp32
+__global__ void k_seq_split_q(bf16* out, const float* q, int kd, size_t units) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= units * kd) return;
+	const size_t u = i / kd, d = i % kd;
+	const float v = q[i];
+	const bf16 hi = __float2bfloat16_rn(v);
+	bf16* r = out + u * 3 * kd;
+	r[d] = hi, r[kd + d] = hi, r[2 * kd + d] = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
 // feed-forward unit on the stacked [gate | up] product.  mode 0: g = min(gate, L), u = clamp(up, -L, L), y = g sigmoid(1.702 g) (u + 1);
 // mode 1: y = silu(gate) up; mode 2: y = gelu(gate) up, gelu(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 // (ld: row stride of gu, 2 * ff when the product holds nothing else)
@@ -306,6 +319,7 @@ struct AttArgs {
 	const int* skip;  // [N] or null: 1 = this token's attention is computed by the product path (k_seq_attn_*), the CTA leaves
 	int nsplit;       // CTAs that share one (token, head tile)'s keys; > 1: partial results go to `part`, k_seq_attention_merge finishes
 	float* part;      // [N][heads][nsplit][vd + 2]: unnormalised output, running maximum, denominator
+	int split = 0;    // 1: on the product path queries, keys and probabilities travel as bf16 pairs (value + remainder), so scores and weights keep fp32 accuracy
 };
 template <typename AT>
 __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* out, SeqBatch sb) {
@@ -507,6 +521,7 @@ struct AttGather {
 	bf16* Vt;   // [vd][Cp]
 	int slot, k0, C, Cp;
 	int kfb;    // the first kfb gathered keys are positions 0 .. kfb-1 (kept first tokens), the rest k0, k0 + 1, ...
+	int split;  // 1: Kb rows are [hi | lo | hi] (3 kd wide: a key as a bf16 value and the bf16 of what the rounding left), Vt rows hold the values twice ([vd][2 Cp])
 };
 __global__ void k_seq_attn_gather(AttGather a, SeqBatch sb) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
@@ -518,14 +533,25 @@ __global__ void k_seq_attn_gather(AttGather a, SeqBatch sb) {
 			const int j = j0 + r, d = d0 + tx;
 			if (j < a.C) {
 				const long row = cache_row(sb, a.slot, j < a.kfb ? j : a.k0 + j - a.kfb);
-				if (d < a.kd) a.Kb[(size_t)j * a.kd + d] = __float2bfloat16_rn(a.kc[row * a.kld + a.kcol + d]);
+				if (d < a.kd) {
+					const float kv = a.kc[row * a.kld + a.kcol + d];
+					const bf16 hi = __float2bfloat16_rn(kv);
+					if (a.split) {
+						bf16* kr = a.Kb + (size_t)j * 3 * a.kd;
+						kr[d] = hi, kr[a.kd + d] = __float2bfloat16_rn(kv - __bfloat162float(hi)), kr[2 * a.kd + d] = hi;
+					} else a.Kb[(size_t)j * a.kd + d] = hi;
+				}
 				tile[r][tx] = d < a.vd ? a.vc[row * a.vld + a.vcol + d] : 0.f;
 			} else tile[r][tx] = 0.f;
 		}
 		__syncthreads();
 		for (int r = ty; r < 32; r += 8) {
 			const int d = d0 + r, j = j0 + tx;
-			if (d < a.vd && j < a.Cp) a.Vt[(size_t)d * a.Cp + j] = __float2bfloat16_rn(tile[tx][r]);
+			if (d < a.vd && j < a.Cp) {
+				const bf16 v = __float2bfloat16_rn(tile[tx][r]);
+				if (a.split) a.Vt[(size_t)d * 2 * a.Cp + j] = v, a.Vt[(size_t)d * 2 * a.Cp + a.Cp + j] = v;
+				else a.Vt[(size_t)d * a.Cp + j] = v;
+			}
 		}
 		__syncthreads();
 	}
@@ -543,6 +569,7 @@ struct AttSoftmax {
 	const bf16* sink; // already offset to the first head of the launch, or null
 	const float* gate; // per head: gate[t * ldg + z], already offset to the first token and head, or null (per-channel gates are applied by the caller)
 	int ldg;
+	int split = 0;     // 1: P rows are 2 Cp wide: the probabilities as bf16, then the bf16 of what that rounding left
 };
 __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
@@ -550,7 +577,7 @@ __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
 	__shared__ float bc;
 	const int t = blockIdx.x, z = blockIdx.y, tid = threadIdx.x;
 	const float* srow = a.S + ((size_t)z * a.T + t) * a.Cp;
-	bf16* prow = a.P + ((size_t)z * a.T + t) * a.Cp;
+	bf16* prow = a.P + ((size_t)z * a.T + t) * a.Cp * (a.split ? 2 : 1);
 	const int qpos = a.qpos0 + t;
 	const int hi = min(a.C - 1, qpos - a.k0 + a.kfb); // last visible column
 	int wlo = a.window > 0 ? qpos - a.window + 1 : 0;
@@ -589,7 +616,12 @@ __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
 	}
 	__syncthreads();
 	const float f = bc;
-	for (int j = tid; j < a.Cp; j += 256) prow[j] = __float2bfloat16_rn(j >= lo && j <= hi && seen(j) ? expf(score(j) - mx) * f : 0.f);
+	for (int j = tid; j < a.Cp; j += 256) {
+		const float p = j >= lo && j <= hi && seen(j) ? expf(score(j) - mx) * f : 0.f;
+		const bf16 ph = __float2bfloat16_rn(p);
+		prow[j] = ph;
+		if (a.split) prow[a.Cp + j] = __float2bfloat16_rn(p - __bfloat162float(ph));
+	}
 }
 
 // ---------------------------------------------------------------- gated delta rule

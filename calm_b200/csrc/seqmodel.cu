@@ -510,37 +510,40 @@ void attention_products(Seq& s, int kind, const AttArgs& a, bf16* out, const Seq
 		if (a.chunk > 0) k0 = std::max(k0, q0 / a.chunk * a.chunk); // the first query's block; later rows mask what lies before theirs
 		const int kfb = a.window > 0 ? std::min(a.keep_first, k0) : 0;
 		const int C = kfb + q0 + Tb - k0, Cp = (C + 7) & ~7;
-		reserve_attn(s, (size_t)C * a.kd, (size_t)a.vd * Cp, (size_t)a.group * Tb * Cp);
+		// split: queries [hi | hi | lo] against keys [hi | lo | hi] (depth 3 kd), probabilities [hi | lo] against the values held twice (depth Cp + C)
+		const int sx = a.split ? 3 : 1, px = a.split ? 2 : 1;
+		reserve_attn(s, (size_t)C * a.kd * sx, (size_t)a.vd * Cp * px, (size_t)a.group * Tb * Cp * px);
 		for (int kvh = 0; kvh < G; ++kvh) {
 			AttGather g;
 			g.kc = a.kc, g.vc = a.vc, g.kld = a.kld, g.vld = a.vld, g.kcol = kvh * a.kd, g.vcol = kvh * a.vd, g.kd = a.kd, g.vd = a.vd;
-			g.Kb = s.att_kb, g.Vt = s.att_vt, g.slot = slot, g.k0 = k0, g.C = C, g.Cp = Cp, g.kfb = kfb;
-			run_kernel(s, kind, (double)C * (a.kd + a.vd) * 6, 0, [&] { launch_k(s, k_seq_attn_gather, dim3(cdiv(Cp, 32), 4), 256, 0, g, sb); });
+			g.Kb = s.att_kb, g.Vt = s.att_vt, g.slot = slot, g.k0 = k0, g.C = C, g.Cp = Cp, g.kfb = kfb, g.split = a.split;
+			run_kernel(s, kind, (double)C * (a.kd + a.vd) * (4 + 2 * sx), 0, [&] { launch_k(s, k_seq_attn_gather, dim3(cdiv(Cp, 32), 4), 256, 0, g, sb); });
 			const int h0 = kvh * a.group;
-			const bf16* q = (const bf16*)s.a3 + ((size_t)(first + t0) * a.heads + h0) * a.kd;
-			gemm(s, q, (long)a.heads * a.kd, a.kd, s.att_kb, a.kd, 0, s.att_s, Cp, (long)Tb * Cp, Tb, C, a.kd, a.group, EPI_F32, nullptr, kind, false);
+			const bf16* q = (const bf16*)s.a3 + ((size_t)(first + t0) * a.heads + h0) * a.kd * sx;
+			gemm(s, q, (long)a.heads * a.kd * sx, a.kd * sx, s.att_kb, a.kd * sx, 0, s.att_s, Cp, (long)Tb * Cp, Tb, C, a.kd * sx, a.group, EPI_F32, nullptr, kind, false);
 			AttSoftmax sm;
 			sm.S = s.att_s, sm.P = s.att_p, sm.T = Tb, sm.C = C, sm.Cp = Cp, sm.qpos0 = q0, sm.k0 = k0, sm.window = a.window, sm.scale = a.scale;
-			sm.keep_first = a.window > 0 ? a.keep_first : 0, sm.kfb = kfb;
+			sm.keep_first = a.window > 0 ? a.keep_first : 0, sm.kfb = kfb, sm.split = a.split;
 			sm.chunk = a.chunk, sm.slopes = a.slopes ? a.slopes + h0 : nullptr, sm.add_one = a.add_one;
 			const bool head_gate = a.gate && a.ges == 0; // one gate per head scales the probabilities; a gate per channel goes into the value product's epilogue
 			sm.sink = a.sink ? a.sink + h0 : nullptr, sm.gate = head_gate ? a.gate + (size_t)(first + t0) * a.ldg + h0 : nullptr, sm.ldg = a.ldg;
 			GemmExtra gx;
 			if (a.gate && !head_gate) gx.gate = a.gate + (size_t)(first + t0) * a.ldg + (size_t)h0 * a.ghs, gx.ldgate = a.ldg, gx.gbs = a.ghs;
-			run_kernel(s, kind, (double)a.group * Tb * Cp * 6, 0, [&] { launch_k(s, k_seq_attn_softmax, dim3(Tb, a.group), 256, 0, sm); });
-			gemm(s, s.att_p, Cp, (long)Tb * Cp, s.att_vt, Cp, 0, out + ((size_t)(first + t0) * a.heads + h0) * a.vd, (long)a.heads * a.vd, a.vd, Tb, a.vd, C, a.group,
-			     EPI_ACT, nullptr, kind, false, &gx);
+			run_kernel(s, kind, (double)a.group * Tb * Cp * (4 + 2 * px), 0, [&] { launch_k(s, k_seq_attn_softmax, dim3(Tb, a.group), 256, 0, sm); });
+			gemm(s, s.att_p, (long)Cp * px, (long)Tb * Cp * px, s.att_vt, (long)Cp * px, 0, out + ((size_t)(first + t0) * a.heads + h0) * a.vd, (long)a.heads * a.vd, a.vd, Tb, a.vd,
+			     a.split ? Cp + C : C, a.group, EPI_ACT, nullptr, kind, false, &gx);
 		}
 		t0 += Tb;
 	}
 }
 
-void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, double kv_rows, int longest, bool products_ok = true) {
+void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, double kv_rows, int longest) {
 	a.skip = nullptr;
 	bool rest = true;
-	if (!s.m.exact && s.attn_products && products_ok && s.n_on_products > 0) {
+	if (!s.m.exact && s.attn_products && s.n_on_products > 0) {
 		const size_t n = (size_t)sb.N * a.heads * a.kd;
-		run_kernel(s, KD_ELEMENT, n * 6.0, 0, [&] { launch_k(s, k_seq_cast_cols<bf16>, cdiv(n, 256), 256, 0, (bf16*)s.a3, a.q, a.heads * a.kd, 0, a.heads * a.kd, sb.N); });
+		if (a.split) run_kernel(s, KD_ELEMENT, n * 10.0, 0, [&] { launch_k(s, k_seq_split_q, cdiv(n, 256), 256, 0, (bf16*)s.a3, a.q, a.kd, (size_t)sb.N * a.heads); });
+		else run_kernel(s, KD_ELEMENT, n * 6.0, 0, [&] { launch_k(s, k_seq_cast_cols<bf16>, cdiv(n, 256), 256, 0, (bf16*)s.a3, a.q, a.heads * a.kd, 0, a.heads * a.kd, sb.N); });
 		for (int b = 0; b < sb.B; ++b)
 			if (s.hb_count[b] >= kAttnGemmMin) attention_products(s, kind, a, (bf16*)out, sb, s.hb_slot[b], s.hb_start[b], s.hb_count[b], s.hb_pos0[b]);
 		a.skip = s.d_skip;
@@ -720,7 +723,8 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		a.gate = L.no_gate ? nullptr : s.proj + H * D + G * D + G * Dv, a.ldg = P, a.ghs = L.gate_per_head ? 1 : Dv, a.ges = L.gate_per_head ? 0 : 1; // a sigmoid gate per output channel (or per head), from the same stacked projection
 		a.chunk = L.chunk, a.slopes = L.dist_bias ? r.slopes : nullptr, a.add_one = L.add_one;
 		const int span = attn_span(L);
-		attention(s, KD_ATTN_WINDOW, a, a2, sb, span > 0 ? std::min(kv_rows, (double)N * span) : kv_rows, longest, !L.scores_f32);
+		a.split = L.scores_f32;
+		attention(s, KD_ATTN_WINDOW, a, a2, sb, span > 0 ? std::min(kv_rows, (double)N * span) : kv_rows, longest);
 		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe, L.b_o);
 	} else if (L.type == SEQ_PAIR) {
 		// two mixers on the same normed input: the first one's product lands scaled in the destination, the second one's is added scaled
@@ -1183,7 +1187,7 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 			if (L.shared_ff > 0) s.w_fsh = std::max(s.w_fsh, (size_t)2 * L.shared_ff + 1 + L.experts + L.ident);
 			s.w_a = std::max(s.w_a, (size_t)L.shared_ff);
 		}
-		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim}); // a3 holds the queries
+		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim * (L.scores_f32 ? 3 : 1)}); // a3 holds the queries (as value + remainder pairs when scores keep fp32 accuracy)
 		if (L.type == SEQ_GLA) s.w_f = std::max({s.w_f, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim}), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.a_rank});
 		if (is_lin(L)) {
 			s.w_f = std::max({s.w_f, (size_t)L.heads * L.dim, (size_t)L.heads * lin_vs(L), (size_t)L.kv_heads * L.dim});

@@ -52,7 +52,7 @@
  * runs in them, pairs included.
  * Options of SEQ_GQA added for them: `qk_per_head` (the query / key RMS norm runs over each head's `dim` channels with one weight
  * vector [dim] shared by the heads), `gate_per_head` (one sigmoid gate per head: `heads` gate rows in w_in), `b_o` (a bias of the
- * output projection), `scores_f32` (scores and softmax weights are kept in fp32 also for prompts).
+ * output projection), `scores_f32` (scores and softmax weights keep fp32 accuracy also where a prompt's attention runs as tensor-core products).
  * Feed-forward SEQ_FF_GATED: down(act(gate) * up) with act = SiLU or the tanh form of GELU (ff_act).
  * Routed experts, further options: `expert_act` 1 -- an expert (and the shared unit) is down(relu(up)^2), without gate rows;
  * route_mode 2 -- scores are sigmoid(router output), the `top` highest are taken, the weights are those scores times route_scale,
@@ -180,7 +180,8 @@ struct SeqLayer {
 	int qk_per_head;       /* 1: q_norm / k_norm are bf16 [dim], the RMS norm runs over each head's channels */
 	int gate_per_head;     /* 1: the gate rows of w_in are `heads` rows, one sigmoid gate per head */
 	const void* b_o;       /* bf16 [width]: bias of the output projection, or NULL (any mixer) */
-	int scores_f32;        /* 1: scores and softmax weights never leave fp32: prompts stay on the fused attention kernel instead of bf16 tensor-core products */
+	int scores_f32;        /* 1: scores and softmax weights keep fp32 accuracy also where prompts run as tensor-core products: queries, keys and probabilities
+	                          travel as bf16 pairs (value + remainder of the rounding), values as bf16 */
 	/* SEQ_FF_GATED */
 	int ff_act;            /* enum SeqFfAct: activation of the gate rows (w_gate_up rows [gate | up]) */
 	/* SEQ_FF_MOE, further options */

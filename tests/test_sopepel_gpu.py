@@ -322,6 +322,34 @@ def test_the_state_remembers_what_the_block_bound_hides():
             assert rel_err(np.concatenate(rows), ref) < TOL["float32"]
 
 
+def test_prompt_attention_as_products_keeps_the_scores_exact(monkeypatch):
+    """bfloat16 mode computes a long portion's attention as tensor-core products over gathered keys, short portions with the fused fp32
+    kernel.  Scores and softmax weights keep fp32 accuracy on both (queries, keys and probabilities travel as bf16 value + remainder
+    pairs), so with sharp scores -- where a key rounded to bf16 alone would move the weights by percents -- the two agree as closely
+    as the rest of the bf16 path allows, also for a portion that continues a cached prefix in the middle of a block of positions; a
+    block size that is one off shows far above that."""
+    for size in (23, 4, 0):
+        cfg = config([pair(size=size, scale=2.0, ls=1.0, rs=0.3, mlp=None), pair(size=0, heads=4, kv_heads=4, dim=8, vdim=8, scale=1.0, mlp=DENSE)])
+        t, toks = weights(cfg, 17), tokens(cfg, 120)
+        ref = plain.forward(cfg, as_f64(t), toks)
+        errs, outs = {}, {}
+        for products in ("1", "0"):
+            monkeypatch.setenv("CALM_B200_SEQ_ATTN_PRODUCTS", products)
+            with sopepel.from_tensors(cfg, t, "bfloat16", max_tokens=300, max_seqs=3, page=8) as m:
+                s1, s2 = m.open(), m.open()
+                a = m.step([s1], [toks[:50]], list(range(50)))
+                b = m.step([s1, s2], [toks[50:], toks[:3]], list(range(73)))  # 70 more tokens on the products path beside a 3-token portion
+                outs[products] = np.concatenate([a, b[:70]])
+                errs[products] = rel_err(outs[products], ref, "bfloat16")
+                assert rel_err(b[70:], ref[:3], "bfloat16") < TOL["bfloat16"]
+        assert errs["1"] < TOL["bfloat16"] and errs["0"] < TOL["bfloat16"] and errs["1"] < 1.5 * errs["0"] + 1e-3
+        if size:
+            for off in (-1, 1):
+                wrong = copy.deepcopy(cfg)
+                wrong["layers"][0]["mixer"]["left"]["mask"]["size"] += off
+                assert rel_err(plain.forward(wrong, as_f64(t), toks), ref) > 4 * errs["1"]
+
+
 def test_tensor_core_products_match_the_warp_level_ones(monkeypatch):
     """bfloat16 mode runs products over many tokens on tcgen05 (the grouped ones of the experts included, with the weight per row and
     the split epilogue of the shared unit's first product) and everything else on mma.sync; same bf16 inputs, fp32 sums in another order."""
