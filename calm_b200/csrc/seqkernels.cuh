@@ -1679,7 +1679,8 @@ struct GemmArgs {
 	long ldgate, gbs;
 	const int* seg;          // grouped products: batch z owns rows [seg[z], seg[z+1]) of X and Y (xbs = ybs = 0), N bounds one group; null: none
 	int x_rows;              // grouped products: rows of X and Y over all groups
-	int split;               // > 0: output columns m >= split leave as relu(acc)^2 in the activation type to Y2[n][m - split] (row stride ldy2), whatever epi says
+	int split;               // > 0: output columns m >= split leave in the activation type to Y2[n][m - split] (row stride ldy2), whatever epi says:
+	int split_act = 0;       //      as relu(acc)^2 (0) or as they are (1)
 	void* Y2;
 	long ldy2;
 	float out_scale = 0.f;   // != 0: the accumulator (after the bias) is multiplied by it
@@ -1709,7 +1710,7 @@ __device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, const GemmR
 	}
 	if (a.split > 0 && m >= a.split) {
 		const float r = fmaxf(acc, 0.f);
-		((AT*)a.Y2)[(size_t)(gr.base + n) * a.ldy2 + (m - a.split)] = to_act<AT>(r * r);
+		((AT*)a.Y2)[(size_t)(gr.base + n) * a.ldy2 + (m - a.split)] = to_act<AT>(a.split_act ? acc : r * r);
 		return;
 	}
 	if (a.epi == EPI_F32) ((float*)a.Y)[o] = acc;

@@ -174,6 +174,13 @@ int proj_stride(const SeqLayer& L) {
 	if (L.in_tail <= 0) return (int)in_rows(L);
 	return (int)((in_rows(L) + (L.ff_kind == SEQ_FF_MOE ? L.in_tail : 0) + 3) & ~(size_t)3);
 }
+// a pair whose own record carries the stacked input matrix: column of the second mixer's first row, and the row stride of the fp32 product
+// (a gated-linear-attention in second place keeps its decay input out of it)
+int pair_offset(const SeqLayer& L) { return (int)((in_rows(L.pair[0]) + 7) & ~(size_t)7); }
+int pair_stride(const SeqLayer& L) {
+	const size_t m = pair_offset(L) + in_rows(L.pair[1]) - (L.pair[1].type == SEQ_GLA ? L.pair[1].a_rank : 0);
+	return (int)((m + 3) & ~(size_t)3);
+}
 int conv_channels(const SeqLayer& L) {
 	if (L.type == SEQ_DELTA) return 2 * L.kv_heads * L.dim + L.heads * L.vdim;
 	if (L.type == SEQ_WINDOW) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim;
@@ -223,6 +230,10 @@ void validate_mixer(const Seq& s, int i, const SeqLayer& L, bool inner) {
 		if (L.type == SEQ_PAIR) {
 			if (inner || !L.pair) CALM_FATAL("seq: layer %d: a pair holds two plain mixers", i);
 			validate_mixer(s, i, L.pair[0], true), validate_mixer(s, i, L.pair[1], true);
+			if (L.w_in)
+				for (int k = 0; k < 2; ++k)
+					if ((L.pair[k].type != SEQ_GQA && L.pair[k].type != SEQ_GLA) || L.pair[k].w_in || L.pair[k].in_tail)
+						CALM_FATAL("seq: layer %d: a pair with a stacked input matrix holds grouped-query and gated linear attention, without input matrices of their own", i);
 			return;
 		}
 		if (L.heads < 1 || L.dim < 1 || L.vdim < 1) CALM_FATAL("seq: layer %d: heads, dim and vdim must be positive", i);
@@ -380,7 +391,8 @@ struct GemmExtra {
 	int x_rows = 0;              // grouped product: rows of X / Y over all groups
 	float epi_f = 0.f;           // EPI_DECAY: exponent
 	float out_scale = 0.f;       // != 0: factor on the accumulator
-	int split = 0;               // columns from here on leave as relu(.)^2 in the activation type to Y2
+	int split = 0;               // columns from here on leave in the activation type to Y2: as relu(.)^2, or unchanged when split_act is 1
+	int split_act = 0;
 	void* Y2 = nullptr;
 	long ldy2 = 0;
 	const float* rs = nullptr;   // a factor per row on the accumulator: rs[(rs_idx ? rs_idx[row] : row) * rs_ld], through a sigmoid when rs_act
@@ -393,7 +405,7 @@ void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, lo
 	GemmArgs a;
 	const GemmExtra none;
 	if (!ex) ex = &none;
-	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows, a.epi_f = ex->epi_f, a.split = ex->split, a.Y2 = ex->Y2, a.ldy2 = ex->ldy2, a.out_scale = ex->out_scale;
+	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows, a.epi_f = ex->epi_f, a.split = ex->split, a.split_act = ex->split_act, a.Y2 = ex->Y2, a.ldy2 = ex->ldy2, a.out_scale = ex->out_scale;
 	a.rs = ex->rs, a.rs_idx = ex->rs_idx, a.rs_ld = ex->rs_ld, a.rs_act = ex->rs_act;
 	a.w_immutable = w_immutable;
 	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
@@ -632,7 +644,7 @@ void out_product(Seq& s, const AT* X, const void* Wt, int N, int K, const OutEpi
 void gla_launch(Seq& s, GlaArgs& g, const SeqBatch& sb, int ld) {
 	const int N = sb.N, H = g.heads, D = g.dim, Dv = g.vdim;
 	g.ldp = ld;
-	g.vec = D % 4 == 0 && Dv % 4 == 0 && ld % 4 == 0 && g.qcol % 4 == 0 && g.kcol % 4 == 0 && g.vcol % 4 == 0; // 16-byte copies; cudaMalloc aligns the bases
+	g.vec = D % 4 == 0 && Dv % 4 == 0 && ld % 4 == 0 && g.qcol % 4 == 0 && g.kcol % 4 == 0 && g.vcol % 4 == 0 && ((uintptr_t)g.proj & 15) == 0; // 16-byte copies
 	g.ldstate = gla_ldstate(D);
 	// lanes per value column: more of them while sequences x heads x columns alone would leave SMs without a CTA
 	int lanes = 4;
@@ -650,10 +662,14 @@ void gla_launch(Seq& s, GlaArgs& g, const SeqBatch& sb, int ld) {
 }
 
 template <typename AT>
-void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest, const OutEpi& oe) {
-	const int N = sb.N, W = s.m.width, P = proj_stride(L);
+void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest, const OutEpi& oe, const float* proj_in = nullptr, int ld_in = 0) {
+	// proj_in: the mixer's input projection has been computed already (a pair's stacked product): its fp32 columns start there, row stride ld_in,
+	// and a gated-linear-attention's decay input (its last rows) waits in a1 in the activation type
+	const int N = sb.N, W = s.m.width, P = proj_in ? ld_in : proj_stride(L);
+	const float* const proj = proj_in ? proj_in : s.proj;
 	AT *hA = (AT*)s.hA, *a1 = (AT*)s.a1, *a2 = (AT*)s.a2;
-	if (L.type != SEQ_PAIR) {
+	bool a1_ready = proj_in != nullptr;
+	if (L.type != SEQ_PAIR && !proj_in) {
 		// one product for everything that reads the normed input: the mixer's rows, and in parallel blocks the router's rows (fp32, behind
 		// the mixer's) or the dense unit's up rows (leaving as relu^2 in the activation type)
 		GemmExtra gx;
@@ -661,6 +677,8 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		int M = (int)in_rows(L);
 		if (L.in_tail > 0 && L.ff_kind == SEQ_FF_MOE) M += L.in_tail;
 		if (L.in_tail > 0 && L.ff_kind == SEQ_FF_RELU2) gx.split = M, gx.Y2 = s.ah, gx.ldy2 = L.ff, M += L.in_tail;
+		if (L.in_tail == 0 && L.type == SEQ_GLA) // the decay's low-rank input (the last rows) leaves the epilogue in the activation type, ready for its second product
+			gx.split = M - L.a_rank, gx.split_act = 1, gx.Y2 = a1, gx.ldy2 = L.a_rank, a1_ready = true;
 		gemm(s, hA, W, 0, L.w_in, W, 0, s.proj, P, 0, N, M, W, 1, EPI_F32, nullptr, -1, true, &gx);
 	}
 	if (L.type == SEQ_LATENT) {
@@ -711,7 +729,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 	} else if (L.type == SEQ_GQA) {
 		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
 		QkArgs qa;
-		qa.proj = s.proj, qa.ldp = P, qa.heads = H, qa.kv_heads = G, qa.dim = D, qa.vdim = Dv, qa.qw = (const bf16*)L.q_norm, qa.kw = (const bf16*)L.k_norm, qa.eps = s.m.eps;
+		qa.proj = proj, qa.ldp = P, qa.heads = H, qa.kv_heads = G, qa.dim = D, qa.vdim = Dv, qa.qw = (const bf16*)L.q_norm, qa.kw = (const bf16*)L.k_norm, qa.eps = s.m.eps;
 		const auto rt = s.rot.find(&L);
 		qa.rot_dims = rt == s.rot.end() ? 0 : L.rot_dims, qa.freq = rt == s.rot.end() ? nullptr : rt->second.first, qa.mag = rt == s.rot.end() ? 1.f : rt->second.second, qa.q = s.f[0], qa.kc = r.cache_a, qa.vc = r.cache_b;
 		qa.v_norm = L.v_norm, qa.per_head = L.qk_per_head;
@@ -720,7 +738,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		AttArgs a;
 		a.q = s.f[0], a.kc = r.cache_a, a.vc = r.cache_b, a.kld = G * D, a.vld = G * Dv, a.heads = H, a.group = H / G, a.tile = attn_tile(H / G, D, Dv), a.kd = D, a.vd = Dv;
 		a.window = L.window, a.keep_first = L.window > 0 ? L.keep_first : 0, a.scale = L.scale, a.sink = nullptr;
-		a.gate = L.no_gate ? nullptr : s.proj + H * D + G * D + G * Dv, a.ldg = P, a.ghs = L.gate_per_head ? 1 : Dv, a.ges = L.gate_per_head ? 0 : 1; // a sigmoid gate per output channel (or per head), from the same stacked projection
+		a.gate = L.no_gate ? nullptr : proj + H * D + G * D + G * Dv, a.ldg = P, a.ghs = L.gate_per_head ? 1 : Dv, a.ges = L.gate_per_head ? 0 : 1; // a sigmoid gate per output channel (or per head), from the same stacked projection
 		a.chunk = L.chunk, a.slopes = L.dist_bias ? r.slopes : nullptr, a.add_one = L.add_one;
 		const int span = attn_span(L);
 		a.split = L.scores_f32;
@@ -731,6 +749,18 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		if (oe.epi != EPI_F32) CALM_FATAL("seq: a pair writes its sum to a buffer of its own");
 		OutEpi first = oe, second = oe;
 		first.scale = L.pair_scale[0], second.epi = EPI_RES, second.res = nullptr, second.scale = L.pair_scale[1];
+		if (L.w_in) {
+			// both mixers' input rows are one matrix (the first's rows padded to a multiple of 8, then the second's): one product; a
+			// gated-linear-attention in second place sends its decay input (the last rows) out in the activation type
+			const int off = pair_offset(L), M = off + (int)in_rows(L.pair[1]), ld = pair_stride(L);
+			GemmExtra gx;
+			gx.bias = L.b_in;
+			if (L.pair[1].type == SEQ_GLA) gx.split = M - L.pair[1].a_rank, gx.split_act = 1, gx.Y2 = a1, gx.ldy2 = L.pair[1].a_rank;
+			gemm(s, hA, W, 0, L.w_in, W, 0, s.proj, ld, 0, N, M, W, 1, EPI_F32, nullptr, -1, true, &gx);
+			mixer_typed<AT>(s, L.pair[0], r.sub[0], sb, kv_rows, longest, first, s.proj, ld);
+			mixer_typed<AT>(s, L.pair[1], r.sub[1], sb, kv_rows, longest, second, s.proj + off, ld);
+			return;
+		}
 		mixer_typed<AT>(s, L.pair[0], r.sub[0], sb, kv_rows, longest, first);
 		mixer_typed<AT>(s, L.pair[1], r.sub[1], sb, kv_rows, longest, second);
 	} else if (is_lin(L)) {
@@ -775,18 +805,19 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 	} else if (L.type == SEQ_GLA) {
 		const int H = L.heads, D = L.dim, Dv = L.vdim;
 		const int cq = 0, ck = H * D, cv = 2 * H * D, cg = cv + H * Dv, ca1 = cg + H * Dv;
-		run_kernel(s, KD_ELEMENT, (double)N * L.a_rank * 6, 0, [&] { launch_k(s, k_seq_cast_cols<AT>, cdiv((long)N * L.a_rank, 256), 256, 0, a1, s.proj, P, ca1, L.a_rank, N); });
+		if (!a1_ready)
+			run_kernel(s, KD_ELEMENT, (double)N * L.a_rank * 6, 0, [&] { launch_k(s, k_seq_cast_cols<AT>, cdiv((long)N * L.a_rank, 256), 256, 0, a1, proj, P, ca1, L.a_rank, N); });
 		{
 			GemmExtra gx; // the decay sigmoid(.)^(1/tau) leaves the product's epilogue in fp32
 			gx.bias = L.b_a2, gx.epi_f = 1.f / L.tau;
 			gemm(s, a1, L.a_rank, 0, L.w_a2, L.a_rank, 0, s.f[3], (long)H * D, 0, N, H * D, L.a_rank, 1, EPI_DECAY, nullptr, -1, true, &gx);
 		}
 		GlaArgs g;
-		g.proj = s.proj, g.ldp = P, g.qcol = cq, g.kcol = ck, g.vcol = cv, g.decay = s.f[3], g.qscale = 1.f / sqrtf((float)D);
+		g.proj = proj, g.ldp = P, g.qcol = cq, g.kcol = ck, g.vcol = cv, g.decay = s.f[3], g.qscale = 1.f / sqrtf((float)D);
 		g.state = r.delta, g.o = s.f[5], g.heads = H, g.dim = D, g.vdim = Dv;
 		gla_launch(s, g, sb, P);
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0, [&] {
-			launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.proj + cg, P, (const bf16*)L.out_norm, N, H, Dv, s.m.eps, 1);
+			launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], proj + cg, P, (const bf16*)L.out_norm, N, H, Dv, s.m.eps, 1);
 		});
 		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe, L.b_o);
 	} else {
@@ -1179,6 +1210,7 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 	std::function<void(const SeqLayer&)> widths = [&](const SeqLayer& L) {
 		if (L.type == SEQ_PAIR) {
 			widths(L.pair[0]), widths(L.pair[1]);
+			if (L.w_in) s.w_proj = std::max(s.w_proj, (size_t)pair_stride(L));
 			return;
 		}
 		if (L.ff > 0 && L.ff_kind == SEQ_FF_MOE) {

@@ -77,8 +77,14 @@ def plan(cfg: dict, tensors: Dict[str, torch.Tensor]) -> Tuple[dict, List[dict],
         if kind != "parallel":
             raise ValueError(f"layer {i}: unknown mixer {kind}")
         m = p + "mix."
-        rec = {"type": seqlib.SEQ_PAIR, "pair": [attention(m + "left.", mx["left"]), linear(m + "right.", mx["right"])],
-               "pair_scale": [float(mx["left_scale"]), float(mx["right_scale"])], "norm1": need(p + "norm1", [width])}
+        left, right = attention(m + "left.", mx["left"]), linear(m + "right.", mx["right"])
+        # both mixers read the same input: their input rows are one matrix (the left's, zero rows up to a multiple of 8, the right's) and one product
+        lw, lb, rw = up.pop(left.pop("w_in")), up.pop(left.pop("b_in")), up.pop(right.pop("w_in"))
+        pad = -lw.shape[0] % 8
+        up[m + "in"] = torch.cat([lw, torch.zeros(pad, width, dtype=torch.bfloat16), rw], 0).contiguous()
+        up[m + "in.b"] = torch.cat([lb, torch.zeros(pad + rw.shape[0], dtype=torch.bfloat16)], 0)
+        rec = {"type": seqlib.SEQ_PAIR, "pair": [left, right], "pair_scale": [float(mx["left_scale"]), float(mx["right_scale"])], "w_in": m + "in", "b_in": m + "in.b",
+               "norm1": need(p + "norm1", [width])}
         ml = lc.get("mlp")
         if ml:
             f = p + "mlp."

@@ -34,7 +34,9 @@
  *               dt = softplus(dt + dt_bias), per head S <- exp(-exp(A_log) dt) S + dt B x^T ([state x vdim]), y = S^T C + D x,
  *               y silu(z), RMS norm in norm_groups equal parts with a weight per channel.  kv_heads = groups of B / C, dim = state.
  *   SEQ_PAIR    two mixers side by side on the same input (`pair` points at two SeqLayer records, their feed-forward unused):
- *               pair_scale[0] * first + pair_scale[1] * second.
+ *               pair_scale[0] * first + pair_scale[1] * second.  When the pair's own record has w_in (and b_in), it holds both mixers'
+ *               input rows as one matrix -- the first's, zero rows up to a multiple of 8, the second's -- for one product; the two
+ *               records then have no w_in of their own (served for SEQ_GQA and SEQ_GLA).
  * Norms (SeqModel.norm_kind): Dynamic Tanh (tanh(alpha x) w + b), or RMS (x / sqrt(mean x^2 + eps) * (w + norm_offset)).
  * Blocks (SeqModel.block): serial -- norm, mixer, norm, residual add, then the same around the feed-forward; parallel -- one
  * norm whose output both the mixer and the feed-forward read, x <- x + (mixer + feed-forward); hyper -- the residual is `streams`

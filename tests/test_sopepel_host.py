@@ -39,10 +39,12 @@ def test_plan_binds_every_size_from_the_config():
     left, right = a["pair"]
     assert left["type"] == seqlib.SEQ_GQA and left["chunk"] == 5 and left["window"] == 0 and left["rot_dims"] == 4 and left["rot_base"] == 100.0
     assert left["qk_per_head"] == left["gate_per_head"] == left["scores_f32"] == 1 and left["kv_heads"] == 2
-    assert up[left["w_in"]].shape == (4 * 8 + 2 * 8 + 2 * 6 + 4, 24) and torch.equal(up[left["w_in"]][-4:], t["l0.mix.left.g"])
-    assert torch.equal(up[left["b_in"]][32:48], t["l0.mix.left.k.b"]) and not up[left["b_in"]][-4:].any()
+    # one input matrix for the pair: the left's 64 rows [q | k | v | g] (a multiple of 8 already), then the right's [q | k | v | g | a1]
+    assert "w_in" not in left and "w_in" not in right and up[a["w_in"]].shape == (64 + 2 * 2 * 4 + 2 * 2 * 10 + 5, 24)
+    assert torch.equal(up[a["w_in"]][60:64], t["l0.mix.left.g"]) and torch.equal(up[a["w_in"]][64:72], t["l0.mix.right.q"]) and torch.equal(up[a["w_in"]][-5:], t["l0.mix.right.a1"])
+    assert torch.equal(up[a["b_in"]][32:48], t["l0.mix.left.k.b"]) and not up[a["b_in"]][60:].any() and up[a["b_in"]].shape == (up[a["w_in"]].shape[0],)
     assert up[left["q_norm"]].shape == (8,) and up[left["b_o"]].shape == (24,)
-    assert right["type"] == seqlib.SEQ_GLA and right["a_rank"] == 5 and right["tau"] == 3.0 and up[right["w_in"]].shape == (2 * 2 * 4 + 2 * 2 * 10 + 5, 24)
+    assert right["type"] == seqlib.SEQ_GLA and right["a_rank"] == 5 and right["tau"] == 3.0
     assert a["ff_kind"] == seqlib.FF_MOE and a["experts"] == 3 and a["top"] == 2 and a["route_mode"] == 2 and a["expert_act"] == a["weight_input"] == a["shared_gate"] == 1
     assert "w_router" not in a and up[a["w_sh_gate_up"]].shape == (1 + 3 + 10, 24)
     assert torch.equal(up[a["w_sh_gate_up"]][:1], t["l0.mlp.shared.sg"]) and torch.equal(up[a["w_sh_gate_up"]][1:4], t["l0.mlp.router"])
