@@ -1430,33 +1430,58 @@ __global__ void __launch_bounds__(V == 4 ? 512 : 1024) k_seq_hc_write(float* x, 
 // Post-norm blocks: x[n] += y / sqrt(mean(y^2) + eps) * (w + offset), where y = base (a sublayer's last product, or null) + the routed
 // experts' sum when `moe.y` is set (choices in order of rank, each times its weight, or times one when moe.wt is null: the weight went
 // in at the expert's input).  The same pass writes the new row of x in the activation type: the input of the sublayer that follows.
-// One CTA per token; a thread keeps its columns of y in registers (rows wider than blockDim * RMS_KEEP form y a second time).
-template <typename AT>
+// One CTA per token.  V = 4: width is a multiple of 4 and a thread owns groups of four neighbouring columns (16-byte loads and stores);
+// V = 1: any width.  A thread keeps PN_KEEP groups of y in registers (wider rows form y a second time).
+#define PN_KEEP 4
+template <typename AT, int V>
+__device__ __forceinline__ void pn_store_act(AT* p, const HcVec<V>& r) {
+	if constexpr (V == 4 && sizeof(AT) == 2) {
+		__nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0], r.v[1]), hi = __floats2bfloat162_rn(r.v[2], r.v[3]);
+		uint2 u;
+		u.x = *reinterpret_cast<unsigned*>(&lo), u.y = *reinterpret_cast<unsigned*>(&hi);
+		*reinterpret_cast<uint2*>(p) = u;
+	} else {
+#pragma unroll
+		for (int e = 0; e < V; ++e) p[e] = to_act<AT>(r.v[e]);
+	}
+}
+template <typename AT, int V>
 __global__ void __launch_bounds__(256) k_seq_post_norm(float* x, AT* act, const float* base, HcMoe moe, const bf16* w, float offset, float eps, int N, int width) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ float red[8];
 	const int tid = threadIdx.x, nt = blockDim.x;
 	const size_t n = blockIdx.x;
 	auto yval = [&](int c) {
-		float y = base ? base[n * width + c] : 0.f;
+		HcVec<V> y;
+#pragma unroll
+		for (int e = 0; e < V; ++e) y.v[e] = 0.f;
+		if (base) y = hc_load<V>(base + n * width + c);
 		if (moe.y)
 			for (int k = 0; k < moe.top; ++k) {
-				const float v = moe.y[(size_t)moe.inv[n * moe.top + k] * width + c];
-				y = moe.wt ? fmaf(moe.wt[n * moe.top + k], v, y) : y + v;
+				const HcVec<V> v = hc_load<V>(moe.y + (size_t)moe.inv[n * moe.top + k] * width + c);
+				const float wk = moe.wt ? moe.wt[n * moe.top + k] : 1.f;
+#pragma unroll
+				for (int e = 0; e < V; ++e) y.v[e] = moe.wt ? fmaf(wk, v.v[e], y.v[e]) : y.v[e] + v.v[e];
 			}
 		return y;
 	};
-	float keep[RMS_KEEP];
+	HcVec<V> keep[PN_KEEP];
 	float ss = 0.f;
 #pragma unroll
-	for (int i = 0; i < RMS_KEEP; ++i) {
-		const int c = i * nt + tid;
-		keep[i] = c < width ? yval(c) : 0.f;
-		ss = fmaf(keep[i], keep[i], ss);
+	for (int i = 0; i < PN_KEEP; ++i) {
+		const int c = (i * nt + tid) * V;
+		if (c < width) keep[i] = yval(c);
+		else {
+#pragma unroll
+			for (int e = 0; e < V; ++e) keep[i].v[e] = 0.f;
+		}
+#pragma unroll
+		for (int e = 0; e < V; ++e) ss = fmaf(keep[i].v[e], keep[i].v[e], ss);
 	}
-	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) {
-		const float y = yval(c);
-		ss = fmaf(y, y, ss);
+	for (int c = (PN_KEEP * nt + tid) * V; c < width; c += nt * V) {
+		const HcVec<V> y = yval(c);
+#pragma unroll
+		for (int e = 0; e < V; ++e) ss = fmaf(y.v[e], y.v[e], ss);
 	}
 	ss = warp_sum(ss);
 	if ((tid & 31) == 0) red[tid >> 5] = ss;
@@ -1466,16 +1491,19 @@ __global__ void __launch_bounds__(256) k_seq_post_norm(float* x, AT* act, const 
 	const float rinv = 1.f / sqrtf(ss / (float)width + eps);
 	float* xr = x + n * width;
 	AT* ar = act + n * width;
-	auto put = [&](int c, float y) {
-		const float v = xr[c] + y * rinv * (ldf(w + c) + offset);
-		xr[c] = v, ar[c] = to_act<AT>(v);
+	auto put = [&](int c, const HcVec<V>& y) {
+		HcVec<V> v = hc_load<V>(xr + c);
+#pragma unroll
+		for (int e = 0; e < V; ++e) v.v[e] += y.v[e] * rinv * (ldf(w + c + e) + offset);
+		hc_store<V>(xr + c, v);
+		pn_store_act<AT, V>(ar + c, v);
 	};
 #pragma unroll
-	for (int i = 0; i < RMS_KEEP; ++i) {
-		const int c = i * nt + tid;
+	for (int i = 0; i < PN_KEEP; ++i) {
+		const int c = (i * nt + tid) * V;
 		if (c < width) put(c, keep[i]);
 	}
-	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) put(c, yval(c));
+	for (int c = (PN_KEEP * nt + tid) * V; c < width; c += nt * V) put(c, yval(c));
 }
 // out[n] = sum of the streams of token n
 __global__ void k_seq_stream_sum(float* out, const float* x, int N, int width, int streams) {

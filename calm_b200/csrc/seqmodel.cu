@@ -613,8 +613,9 @@ template <typename AT>
 void post_norm(Seq& s, const float* base, const HcMoe& moe, const SeqNorm& nm, int N) {
 	const int W = s.m.width;
 	run_kernel(s, KD_NORM, (double)N * W * (8.0 + (base ? 4 : 0) + (moe.y ? 4.0 * moe.top : 0) + act_size(s)), 0, [&] {
-		const int threads = std::min(256, std::max(32, cdiv(W, 4 * 32) * 32));
-		launch_k(s, k_seq_post_norm<AT>, N, threads, 0, s.x, (AT*)s.hA, base, moe, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, N, W);
+		if (W % 4 == 0) // a group of four neighbouring columns per thread up to 1024 columns, whole warps
+			launch_k(s, k_seq_post_norm<AT, 4>, N, std::min(256, cdiv(W / 4, 32) * 32), 0, s.x, (AT*)s.hA, base, moe, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, N, W);
+		else launch_k(s, k_seq_post_norm<AT, 1>, N, std::min(256, cdiv(W, 32) * 32), 0, s.x, (AT*)s.hA, base, moe, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, N, W);
 	});
 }
 // write the streams from a sublayer's output; with next_in / next_norm also the normed input of the sublayer that follows (into hA)

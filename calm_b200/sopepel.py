@@ -83,7 +83,7 @@ def plan(cfg: dict, tensors: Dict[str, torch.Tensor]) -> Tuple[dict, List[dict],
         pad = -lw.shape[0] % 8
         up[m + "in"] = torch.cat([lw, torch.zeros(pad, width, dtype=torch.bfloat16), rw], 0).contiguous()
         up[m + "in.b"] = torch.cat([lb, torch.zeros(pad + rw.shape[0], dtype=torch.bfloat16)], 0)
-        rec = {"type": seqlib.SEQ_PAIR, "pair": [left, right], "pair_scale": [float(mx["left_scale"]), float(mx["right_scale"])], "w_in": m + "in", "b_in": m + "in.b",
+        rec = {"type": seqlib.SEQ_PAIR, "pair": [left, right], "pair_scale": [float(mx.get("left_scale", 1.0)), float(mx.get("right_scale", 1.0))], "w_in": m + "in", "b_in": m + "in.b",
                "norm1": need(p + "norm1", [width])}
         ml = lc.get("mlp")
         if ml:

@@ -109,8 +109,8 @@ def right_linear(t, m: str, mx: dict, h: np.ndarray, eps: float) -> np.ndarray:
 
 
 def mixer(t, p: str, mx: dict, h: np.ndarray, eps: float) -> np.ndarray:
-    return float(mx["left_scale"]) * left_attention(t, p + "mix.left.", mx["left"], h, eps) + \
-        float(mx["right_scale"]) * right_linear(t, p + "mix.right.", mx["right"], h, eps)
+    return float(mx.get("left_scale", 1.0)) * left_attention(t, p + "mix.left.", mx["left"], h, eps) + \
+        float(mx.get("right_scale", 1.0)) * right_linear(t, p + "mix.right.", mx["right"], h, eps)
 
 
 def dense_unit(t, f: str, h: np.ndarray) -> np.ndarray:
