@@ -466,8 +466,9 @@ def test_trace_replay_from_a_model_folder(tmp_path, dtype):
     (folder / "config.json").write_text(json.dumps(cfg))
     container.write_tensors(str(folder / "model.safetensors"), t)
     assert registry.architecture_of(str(folder)) == "Sopepel"
-    # (request c takes other tokens than seed 3 would give: that seed's first token leaves the first mixer an output that nearly cancels, and the
-    # norm behind it then magnifies bf16 rounding sixtyfold -- float32 shows the same row at ten times the others' error)
+    # (request c takes other tokens than seed 3 would give.  At a sequence's first token the linear attention reads out (q.k) v, and the norm
+    # behind it leaves sign(q.k) v / rms(v): for that seed's first token one head has q.k = -0.001 against |q||k| = 3.7, so bf16 rounding
+    # decides the sign of that head's whole output -- float32 shows the same row at ten times the others' error)
     reqs = {"a": tokens(cfg, 46, 1), "b": tokens(cfg, 9, 2), "c": tokens(cfg, 4, 7), "d": tokens(cfg, 30, 4), "e": tokens(cfg, 2, 5)}
     steps = [{"step": 0, "entries": [{"id": "a", "tokens": reqs["a"][:40], "want": [0, 17, 39]}, {"id": "b", "tokens": reqs["b"][:6], "want": [5]},
                                      {"id": "c", "tokens": reqs["c"][:1], "want": [0]}], "end": []}]
